@@ -58,10 +58,11 @@ class StorageGroup:
         shape = (len(self.entries), num_pages, need.kv_heads, PAGE, need.head_dim)
         # zeroed once: kernels multiply masked positions of a page by zero, which must not meet a NaN
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        v_dim = need.head_dim if need.v_head_dim is None else need.v_head_dim
+        self.v = torch.zeros(shape[:-1] + (v_dim,), dtype=dtype, device=device)   # no storage with v_head_dim = 0
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class Cache:

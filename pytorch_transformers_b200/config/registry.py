@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class and model builder.
 
 Lookup goes by config.json's ``model_type`` first and by its ``architectures`` second, as
-``AutoConfig`` / ``AutoModelForCausalLM`` do
+(or its single ``architecture``) second, as ``AutoConfig`` / ``AutoModelForCausalLM`` do
 (src/transformers/models/auto/configuration_auto.py:1073-1088, auto_factory.py:387-400); an
 unknown name is a ValueError that lists what is registered (configuration_auto.py:1095-1099).
 """
@@ -47,10 +47,13 @@ def lookup(raw_config: Dict[str, Any]) -> Architecture:
     mt = raw_config.get("model_type")
     if mt in _BY_TYPE:
         return _BY_TYPE[mt]
-    for a in raw_config.get("architectures") or ():
+    named = list(raw_config.get("architectures") or ())
+    if isinstance(raw_config.get("architecture"), str):     # some designs name themselves in one string
+        named.append(raw_config["architecture"])
+    for a in named:
         if a in _BY_CLASS:
             return _BY_CLASS[a]
-    raise ValueError(f"unrecognised model: model_type={mt!r}, architectures={raw_config.get('architectures')!r}. "
+    raise ValueError(f"unrecognised model: model_type={mt!r}, architectures={named!r}. "
                      f"Registered model types: {', '.join(sorted(_BY_TYPE)) or 'none'}; architectures: "
                      f"{', '.join(sorted(_BY_CLASS)) or 'none'}")
 

@@ -1,0 +1,347 @@
+// Latent attention over the paged cache: every token caches one row [latent c (rank) | shared rotated
+// key part (rot_dim)] that all heads read. With the key up-projection folded into the query
+// (q_abs[h] = W_uk[h]^T q_plain[h]) a head's score against a cached row is
+//   (q_abs[h] . c + q_rot[h] . k_rot) * scale
+// and its output in latent space is sum_j p_j c_j; the value up-projection follows outside.
+// So the heads of a token are rows of one tile over the same cached rows, and the values are the
+// first `rank` entries of the keys: a page is staged once and used for scores and for outputs.
+// All arithmetic is float32 on the CUDA cores; keys are reduced in blocks of 64 aligned to absolute
+// positions in ascending order, so a position's result does not depend on how its tokens were cut
+// into steps or batched.
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROWS = 16;      // (token, head) rows of a tile
+constexpr int THREADS = 128;  // 8 threads per row
+
+// One block per token: the row `src` [rank + rot_dim] of the down-projection becomes the cached row:
+// the first `rank` entries divided by their root mean square (eps inside the root) times norm_w,
+// the last rot_dim rotated by the token's position (pairs (2i, 2i+1) when interleaved, else
+// (i, i + rot_pairs)); entries past 2 * rot_pairs pass unchanged.
+template <typename T>
+__global__ void latent_store_kernel(const T* __restrict__ src, long long src_stride, const float* __restrict__ norm_w,
+                                    float eps, T* __restrict__ pool, StepBatch sb, const float* __restrict__ rope_cos,
+                                    const float* __restrict__ rope_sin, int rot_pairs, int interleaved, int rank,
+                                    int rot_dim) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int pos = sb.tok_pos[t], seq = sb.tok_seq[t];
+  const int page = sb.pages[size_t(seq) * sb.pages_stride + pos / PTB_PAGE];
+  const T* row = src + size_t(t) * src_stride;
+  T* dst = pool + kv_offset(page, 0, pos % PTB_PAGE, 1, rank + rot_dim);
+  float q = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+    const float v = to_f(row[i]);
+    q += v * v;
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(q, scratch) / float(rank) + eps);
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f<T>(to_f(row[i]) * rstd * norm_w[i]);
+  const int items = rot_pairs + (rot_dim - 2 * rot_pairs);
+  for (int e = threadIdx.x; e < items; e += blockDim.x) {
+    if (e < rot_pairs) {
+      const int ia = interleaved ? 2 * e : e, ib = interleaved ? 2 * e + 1 : e + rot_pairs;
+      float a, b;
+      rotate_pair(to_f(row[rank + ia]), to_f(row[rank + ib]), rope_cos[size_t(t) * rot_pairs + e],
+                  rope_sin[size_t(t) * rot_pairs + e], a, b);
+      dst[rank + ia] = from_f<T>(a);
+      dst[rank + ib] = from_f<T>(b);
+    } else {
+      const int i = 2 * rot_pairs + (e - rot_pairs);
+      dst[rank + i] = row[rank + i];
+    }
+  }
+}
+
+// One block = one tile (tile_tokens consecutive new tokens of a sequence) x one chunk of
+// heads_per_block heads x one split of the key pages; tile_tokens * heads_per_block <= ROWS.
+//   q_abs [tokens, heads, rank] float32: queries with the key up-projection folded in
+//   q     [tokens, heads, q_dim]: the projection's rows; the part to rotate starts at q_rot_off
+//   pool  [pages][64][rank + rot_dim]
+//   out   [tokens, heads, rank]: softmax-weighted sums of the latents
+// With n_splits > 1 a block writes (max, sum, unnormalised sums) of its pages to `part` and
+// latent_join_kernel merges the splits in order.
+template <typename T, int DPT>
+__global__ void __launch_bounds__(THREADS)
+latent_attention_kernel(const float* __restrict__ q_abs, const T* __restrict__ q, int q_dim, int q_rot_off,
+                        const T* __restrict__ pool, float* __restrict__ part, T* __restrict__ out, StepBatch sb,
+                        const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
+                        const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int rot_pairs,
+                        int interleaved, int heads, int rank, int rot_dim, int tile_tokens, int heads_per_block,
+                        float scale, int n_splits) {
+  extern __shared__ float smem[];
+  const int dk = rank + rot_dim, qstride = dk + 1, kstride = dk + 1;
+  float* qs = smem;                       // [ROWS][dk + 1]
+  float* kv = qs + ROWS * qstride;        // [64][dk + 1]
+  float* ps = kv + PTB_PAGE * kstride;    // [ROWS][64]
+
+  const int tile = blockIdx.x, h0 = blockIdx.y * heads_per_block, split = blockIdx.z;
+  const int seq = tile_seq[tile], q0 = tile_q0[tile];
+  const int n_new = sb.seq_new[seq], past = sb.seq_past[seq], start = sb.seq_start[seq];
+  const int toks = min(tile_tokens, n_new - q0);
+  const int tid = threadIdx.x, r = tid / 8, c = tid % 8;
+  const int my_tok = r / heads_per_block, my_head = h0 + r % heads_per_block;
+  const bool my_row = my_tok < toks && my_head < heads && r < tile_tokens * heads_per_block;
+  const int my_pos = my_row ? past + q0 + my_tok : -1;
+
+  for (int i = tid; i < ROWS * rank; i += THREADS) {
+    const int rr = i / rank, e = i % rank;
+    const int ti = rr / heads_per_block, hh = h0 + rr % heads_per_block;
+    const bool ok = ti < toks && hh < heads && rr < tile_tokens * heads_per_block;
+    qs[rr * qstride + e] = ok ? q_abs[(size_t(start + q0 + ti) * heads + hh) * rank + e] : 0.f;
+  }
+  const int items = rot_pairs + (rot_dim - 2 * rot_pairs);
+  for (int i = tid; i < ROWS * items; i += THREADS) {
+    const int rr = i / items, e = i % items;
+    const int ti = rr / heads_per_block, hh = h0 + rr % heads_per_block;
+    const bool ok = ti < toks && hh < heads && rr < tile_tokens * heads_per_block;
+    const size_t tok = size_t(start + q0 + ti);
+    const T* src = q + (tok * heads + hh) * q_dim + q_rot_off;
+    float* dst = qs + rr * qstride + rank;
+    if (e < rot_pairs) {
+      const int ia = interleaved ? 2 * e : e, ib = interleaved ? 2 * e + 1 : e + rot_pairs;
+      float a = 0.f, b = 0.f;
+      if (ok) rotate_pair(to_f(src[ia]), to_f(src[ib]), rope_cos[tok * rot_pairs + e], rope_sin[tok * rot_pairs + e], a, b);
+      dst[ia] = a;
+      dst[ib] = b;
+    } else {
+      const int j = 2 * rot_pairs + (e - rot_pairs);
+      dst[j] = ok ? to_f(src[j]) : 0.f;
+    }
+  }
+
+  float acc[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) acc[i] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+
+  const int last_pos = past + q0 + toks - 1;
+  const int n_blocks = last_pos / PTB_PAGE + 1;
+  const int per = (n_blocks + n_splits - 1) / n_splits;
+  const int kb_lo = split * per, kb_hi = min(n_blocks, kb_lo + per) - 1;
+  const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
+  const bool vec = sizeof(T) == 2 && dk % 8 == 0 && aligned16(pool);
+
+  for (int kb = kb_lo; kb <= kb_hi; ++kb) {
+    const int valid = min(PTB_PAGE, last_pos + 1 - kb * PTB_PAGE);
+    const T* kp = pool + kv_offset(pages[kb], 0, 0, 1, dk);
+    __syncthreads();  // the page before and its weights are no longer read (and qs is written)
+    if (vec) {
+      const int chunks = dk / 8;
+      for (int i = tid; i < PTB_PAGE * chunks; i += THREADS) {
+        const int j = i / chunks, e = (i % chunks) * 8;
+        float f[8];
+        if (j < valid) {
+          unpack_bf16x8(*reinterpret_cast<const uint4*>(kp + size_t(j) * dk + e), f);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) f[u] = 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) kv[j * kstride + e + u] = f[u];
+      }
+    } else {
+      for (int i = tid; i < PTB_PAGE * dk; i += THREADS) {
+        const int j = i / dk, e = i % dk;
+        kv[j * kstride + e] = (j < valid) ? to_f(kp[i]) : 0.f;
+      }
+    }
+    __syncthreads();
+    // scores: this thread owns keys j = c + 8 jj of row r
+    float s[8];
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) s[jj] = 0.f;
+    const float* qr = qs + r * qstride;
+    for (int e = 0; e < dk; ++e) {
+      const float qe = qr[e];
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) s[jj] = fmaf(qe, kv[(c + 8 * jj) * kstride + e], s[jj]);
+    }
+    float m_blk = -INFINITY;
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      const int key_pos = kb * PTB_PAGE + c + 8 * jj;
+      s[jj] = (key_pos <= my_pos) ? s[jj] * scale : -INFINITY;
+      m_blk = fmaxf(m_blk, s[jj]);
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) m_blk = fmaxf(m_blk, __shfl_xor_sync(0xffffffffu, m_blk, o));
+    const float m_new = fmaxf(m_run, m_blk);
+    float corr = 1.f, l_blk = 0.f;
+    if (m_new == -INFINITY) {
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) ps[r * PTB_PAGE + c + 8 * jj] = 0.f;
+    } else {
+      corr = (m_run == -INFINITY) ? 0.f : expf(m_run - m_new);
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        const float p = (s[jj] == -INFINITY) ? 0.f : expf(s[jj] - m_new);
+        ps[r * PTB_PAGE + c + 8 * jj] = p;
+        l_blk += p;
+      }
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) l_blk += __shfl_xor_sync(0xffffffffu, l_blk, o);
+    l_run = l_run * corr + l_blk;
+    m_run = m_new;
+    __syncwarp();  // a row's weights are written and read by the 8 threads of one warp
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) acc[i] *= corr;
+    for (int j = 0; j < PTB_PAGE; ++j) {
+      const float p = ps[r * PTB_PAGE + j];
+      const float* vr = kv + j * kstride;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) {
+        const int e = c + 8 * i;
+        if (e < rank) acc[i] = fmaf(p, vr[e], acc[i]);
+      }
+    }
+  }
+  if (n_splits > 1) {
+    float* p = part + ((size_t(tile) * gridDim.y + blockIdx.y) * n_splits + split) * ROWS * size_t(rank + 2) +
+               size_t(r) * (rank + 2);
+    if (c == 0) {
+      p[0] = m_run;
+      p[1] = l_run;
+    }
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int e = c + 8 * i;
+      if (e < rank) p[2 + e] = acc[i];
+    }
+    return;
+  }
+  if (my_row) {
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    T* o = out + (size_t(start + q0 + my_tok) * heads + my_head) * rank;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int e = c + 8 * i;
+      if (e < rank) o[e] = from_f<T>(acc[i] * inv);
+    }
+  }
+}
+
+// merges the splits of a tile in ascending order of their pages
+template <typename T>
+__global__ void latent_join_kernel(const float* __restrict__ part, T* __restrict__ out, StepBatch sb,
+                                   const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int heads,
+                                   int rank, int tile_tokens, int heads_per_block, int n_splits) {
+  const int tile = blockIdx.x, h0 = blockIdx.y * heads_per_block;
+  const int seq = tile_seq[tile], q0 = tile_q0[tile];
+  const int toks = min(tile_tokens, sb.seq_new[seq] - q0), start = sb.seq_start[seq];
+  const float* base = part + (size_t(tile) * gridDim.y + blockIdx.y) * n_splits * ROWS * size_t(rank + 2);
+  for (int i = threadIdx.x; i < ROWS * rank; i += blockDim.x) {
+    const int r = i / rank, e = i % rank;
+    const int ti = r / heads_per_block, hh = h0 + r % heads_per_block;
+    if (!(ti < toks && hh < heads && r < tile_tokens * heads_per_block)) continue;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, base[(size_t(s) * ROWS + r) * (rank + 2)]);
+    float l = 0.f, o = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float* p = base + (size_t(s) * ROWS + r) * (rank + 2);
+      if (p[0] == -INFINITY) continue;
+      const float w = expf(p[0] - m);
+      l += p[1] * w;
+      o += p[2 + e] * w;
+    }
+    out[(size_t(start + q0 + ti) * heads + hh) * rank + e] = from_f<T>(l > 0.f ? o / l : 0.f);
+  }
+}
+
+template <typename T, int DPT>
+int launch_latent(const float* q_abs, const void* q, int q_dim, int q_rot_off, const void* pool, float* part,
+                  void* out, const StepBatch& sb, const int* tile_seq, const int* tile_q0, int n_tiles,
+                  const float* rope_cos, const float* rope_sin, int rot_pairs, int interleaved, int heads, int rank,
+                  int rot_dim, int tile_tokens, int heads_per_block, float scale, int n_splits, cudaStream_t stream) {
+  const int dk = rank + rot_dim;
+  const size_t smem = sizeof(float) * (size_t(ROWS) * (dk + 1) + size_t(PTB_PAGE) * (dk + 1) + ROWS * PTB_PAGE);
+  if (smem > 220 * 1024) return PTB_ERR_SIZE;
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(latent_attention_kernel<T, DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(smem)) != cudaSuccess)
+      return PTB_ERR_LAUNCH;
+    configured = smem;
+  }
+  const int chunks = (heads + heads_per_block - 1) / heads_per_block;
+  dim3 grid(n_tiles, chunks, n_splits);
+  latent_attention_kernel<T, DPT><<<grid, THREADS, smem, stream>>>(
+      q_abs, (const T*)q, q_dim, q_rot_off, (const T*)pool, part, (T*)out, sb, tile_seq, tile_q0, rope_cos, rope_sin,
+      rot_pairs, interleaved, heads, rank, rot_dim, tile_tokens, heads_per_block, scale, n_splits);
+  int rc = launch_status();
+  if (rc != PTB_OK || n_splits <= 1) return rc;
+  latent_join_kernel<T><<<dim3(n_tiles, chunks), 256, 0, stream>>>(part, (T*)out, sb, tile_seq, tile_q0, heads, rank,
+                                                                  tile_tokens, heads_per_block, n_splits);
+  return launch_status();
+}
+
+template <typename T>
+int dispatch_latent(const float* q_abs, const void* q, int q_dim, int q_rot_off, const void* pool, float* part,
+                    void* out, const StepBatch& sb, const int* tile_seq, const int* tile_q0, int n_tiles,
+                    const float* rope_cos, const float* rope_sin, int rot_pairs, int interleaved, int heads, int rank,
+                    int rot_dim, int tile_tokens, int heads_per_block, float scale, int n_splits,
+                    cudaStream_t stream) {
+#define PTB_LATENT(D)                                                                                             \
+  return launch_latent<T, D>(q_abs, q, q_dim, q_rot_off, pool, part, out, sb, tile_seq, tile_q0, n_tiles, rope_cos, \
+                             rope_sin, rot_pairs, interleaved, heads, rank, rot_dim, tile_tokens, heads_per_block,  \
+                             scale, n_splits, stream)
+  if (rank <= 64) PTB_LATENT(8);
+  if (rank <= 128) PTB_LATENT(16);
+  if (rank <= 256) PTB_LATENT(32);
+  PTB_LATENT(64);
+#undef PTB_LATENT
+}
+
+}  // namespace
+
+PTB_API int ptb_latent_rows() { return ROWS; }
+
+// float32 values of workspace that ptb_latent_attention needs with n_splits > 1
+PTB_API long long ptb_latent_part_floats(int n_tiles, int heads, int heads_per_block, int n_splits, int rank) {
+  if (n_splits <= 1) return 0;
+  const long long chunks = (heads + heads_per_block - 1) / heads_per_block;
+  return (long long)n_tiles * chunks * n_splits * ROWS * (rank + 2);
+}
+
+PTB_API int ptb_latent_store(int dtype, const void* src, long long src_stride, const float* norm_w, float eps,
+                             void* pool, const StepBatch* sb, const float* rope_cos, const float* rope_sin,
+                             int rot_pairs, int interleaved, int rank, int rot_dim, cudaStream_t stream) {
+  if (sb->n_tokens <= 0) return PTB_OK;
+  if (rank <= 0 || rot_dim < 0 || rot_pairs < 0 || 2 * rot_pairs > rot_dim) return PTB_ERR_SIZE;
+  if (rot_pairs > 0 && (rope_cos == nullptr || rope_sin == nullptr)) return PTB_ERR_SIZE;
+  if (dtype == PTB_F32)
+    latent_store_kernel<float><<<sb->n_tokens, 128, 0, stream>>>((const float*)src, src_stride, norm_w, eps,
+                                                                 (float*)pool, *sb, rope_cos, rope_sin, rot_pairs,
+                                                                 interleaved, rank, rot_dim);
+  else if (dtype == PTB_BF16)
+    latent_store_kernel<__nv_bfloat16><<<sb->n_tokens, 128, 0, stream>>>(
+        (const __nv_bfloat16*)src, src_stride, norm_w, eps, (__nv_bfloat16*)pool, *sb, rope_cos, rope_sin, rot_pairs,
+        interleaved, rank, rot_dim);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}
+
+PTB_API int ptb_latent_attention(int dtype, const float* q_abs, const void* q, int q_dim, int q_rot_off,
+                                 const void* pool, float* part, void* out, const StepBatch* sb, const int* tile_seq,
+                                 const int* tile_q0, int n_tiles, const float* rope_cos, const float* rope_sin,
+                                 int rot_pairs, int interleaved, int heads, int rank, int rot_dim, int tile_tokens,
+                                 int heads_per_block, float scale, int n_splits, cudaStream_t stream) {
+  if (n_tiles <= 0) return PTB_OK;
+  if (heads <= 0 || rank <= 0 || rank > 512 || rot_dim < 0 || rot_pairs < 0 || 2 * rot_pairs > rot_dim ||
+      tile_tokens <= 0 || heads_per_block <= 0 || tile_tokens * heads_per_block > ROWS || n_splits < 1 ||
+      n_splits > 65535 || (heads + heads_per_block - 1) / heads_per_block > 65535)
+    return PTB_ERR_SIZE;
+  if (n_splits > 1 && part == nullptr) return PTB_ERR_SIZE;
+  if (rot_pairs > 0 && (rope_cos == nullptr || rope_sin == nullptr)) return PTB_ERR_SIZE;
+  if (dtype == PTB_F32)
+    return dispatch_latent<float>(q_abs, q, q_dim, q_rot_off, pool, part, out, *sb, tile_seq, tile_q0, n_tiles,
+                                  rope_cos, rope_sin, rot_pairs, interleaved, heads, rank, rot_dim, tile_tokens,
+                                  heads_per_block, scale, n_splits, stream);
+  if (dtype == PTB_BF16)
+    return dispatch_latent<__nv_bfloat16>(q_abs, q, q_dim, q_rot_off, pool, part, out, *sb, tile_seq, tile_q0, n_tiles,
+                                          rope_cos, rope_sin, rot_pairs, interleaved, heads, rank, rot_dim,
+                                          tile_tokens, heads_per_block, scale, n_splits, stream);
+  return PTB_ERR_DTYPE;
+}

@@ -246,6 +246,14 @@ class StepContext:
             c.seq_past, c.pages = self.dev["seq_past"].data_ptr(), self.dev[f"pages{gi}"].data_ptr()
             c.pages_stride, c.n_tokens, c.n_seqs = tab.shape[1], self.n_tokens, self.n_seqs
             self.batch_c.append(c)
+        if not tables:
+            # a model without paged entries (every mixer keeps fixed-size state): the counts and positions alone
+            c = K.StepBatchC()
+            c.tok_seq, c.tok_pos = self.dev["tok_seq"].data_ptr(), self.dev["tok_pos"].data_ptr()
+            c.seq_start, c.seq_new = self.dev["seq_start"].data_ptr(), self.dev["seq_new"].data_ptr()
+            c.seq_past, c.pages = self.dev["seq_past"].data_ptr(), 0
+            c.pages_stride, c.n_tokens, c.n_seqs = 0, self.n_tokens, self.n_seqs
+            self.batch_c.append(c)
 
     def begin_forward(self) -> None:
         """Forget what an earlier forward pass over this step computed (a step that is captured as a

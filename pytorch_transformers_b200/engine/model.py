@@ -365,6 +365,8 @@ class CausalLM:
             k.scale_(x, self.spec.embedding_scale)
         if self.embedding_norm is not None:
             x = self.embedding_norm.forward(x)
+        if self.spec.stream_float32 and x.dtype != torch.float32:
+            x = k.to_float(x)       # from here to the final norm the stream is float32
         for entry in self.schedule:
             x = self.blocks[entry.block].forward(x, ctx, entry)   # a tensor, or a DeferredSum of two branches
         x = resolve(k, x)

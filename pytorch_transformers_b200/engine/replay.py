@@ -65,14 +65,17 @@ def main(argv=None) -> int:
                     help="bfloat16: the kernels and precisions of serving; float32: everything in true 32-bit")
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens held by live requests at one time (each rounded up to 64); sizes the cache")
+                    help="most tokens held by live requests at one time; sizes the cache")
     args = ap.parse_args(argv)
     print("trace_run: loading the library (kernels are compiled at first use)", file=sys.stderr, flush=True)
+    from ..cache.paged import PAGE
     from ..modeling import AutoModelForCausalLM
     from .. import native
     native.library()
     model = AutoModelForCausalLM.from_pretrained(args.model, dtype=args.dtype, device="cuda")
-    cache = model.new_cache(max(args.max_tokens, 64))
+    # the count is of tokens; every live request rounds its own up to a whole page, so there is room for
+    # that remainder of many requests
+    cache = model.new_cache(max(args.max_tokens, 64) + 64 * PAGE)
     print("trace_run: ready", file=sys.stderr, flush=True)
     replay(model, cache, sys.stdin, args.out)
     return 0

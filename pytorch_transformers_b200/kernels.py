@@ -81,8 +81,13 @@ def lib():
                      "ptb_rope_table", "ptb_attention_decode", "ptb_attention_tc", "ptb_attention_tc_supports",
                      "ptb_attention_tc_tile_tokens", "ptb_tc_linear", "ptb_tc_linear_max_rows",
                      "ptb_tc_linear_k_multiple", "ptb_attention_decode_tc", "ptb_attention_decode_tc_supports",
-                     "ptb_fill_normal", "ptb_selftest_bounded_wait", "ptb_scale", "ptb_selftest_mma_cadence"):
+                     "ptb_fill_normal", "ptb_selftest_bounded_wait", "ptb_scale", "ptb_selftest_mma_cadence",
+                     "ptb_norm_stream", "ptb_add_stream", "ptb_latent_store", "ptb_latent_attention", "ptb_latent_rows",
+                     "ptb_rglru_conv", "ptb_rglru_scan", "ptb_block_linear", "ptb_route", "ptb_expert_plan",
+                     "ptb_expert_linear", "ptb_expert_combine"):
             getattr(L, name).restype = ctypes.c_int
+        L.ptb_latent_part_floats.restype = ctypes.c_longlong
+        L.ptb_expert_plan_words.restype = ctypes.c_longlong
         _configured = True
     return L
 
@@ -629,3 +634,200 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+# ------------------------------------------------------------------------------------------------
+# A float32 residual stream beside bfloat16 matrices
+def norm_stream(x: torch.Tensor, gain: torch.Tensor, bias: Optional[torch.Tensor], eps: float, kind: str,
+                out_dtype: torch.dtype, addend: Optional[torch.Tensor] = None):
+    """Norm of float32 rows ``x`` (or of ``x + addend``, addend float32 or bfloat16) written in ``out_dtype``.
+    Returns ``y``, or ``(sum, y)`` with the float32 sum when ``addend`` is given."""
+    _need_cuda(x, gain, bias, addend)
+    if x.dtype != torch.float32:
+        raise KernelError("norm_stream takes a float32 stream")
+    n, width = x.shape
+    y = torch.empty((n, width), dtype=out_dtype, device=x.device)
+    total = torch.empty_like(x) if addend is not None else None
+    _check(lib().ptb_norm_stream(_ptr(x), 0 if addend is None else _dtype_code(addend), _ptr(addend), _ptr(total),
+                                 _ptr(gain), _ptr(bias), _dtype_code(y), _ptr(y), n, width, ctypes.c_float(eps),
+                                 NORM_KINDS[kind], _stream(x)), "norm_stream")
+    return y if addend is None else (total, y)
+
+
+def add_stream(x: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
+    """x + a in float32: ``x`` is the float32 stream, ``a`` a branch's result in float32 or bfloat16."""
+    _need_cuda(x, a)
+    if x.dtype != torch.float32 or x.shape != a.shape:
+        raise KernelError("add_stream takes a float32 stream and an addend of its shape")
+    out = torch.empty_like(x)
+    _check(lib().ptb_add_stream(_ptr(x), _dtype_code(a), _ptr(a), _ptr(out), ctypes.c_longlong(x.numel()), _stream(x)),
+           "add_stream")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Latent attention
+LATENT_ROWS = 16   # ptb_latent_rows(): (token, head) rows of a tile
+
+
+def latent_store(src: torch.Tensor, norm_w: torch.Tensor, eps: float, pool: torch.Tensor, batch: StepBatchC, rope,
+                 rank: int, rot_dim: int, interleaved: bool = True) -> None:
+    """Rows ``src`` [tokens, rank + rot_dim] (a view whose rows may be wider apart) of the latent
+    down-projection become cache rows: the first ``rank`` RMS-normed with ``norm_w``, the rest rotated by
+    the tokens' positions (``rope`` = (cos, sin) [tokens, pairs])."""
+    _need_cuda(norm_w, pool)
+    if src.stride(1) != 1 or src.shape[1] != rank + rot_dim or pool.shape[-1] != rank + rot_dim or pool.dtype != src.dtype:
+        raise KernelError("latent_store: the rows or the pool do not fit rank + rot_dim")
+    cos, sin = rope if rope is not None else (None, None)
+    pairs = 0 if cos is None else cos.shape[1]
+    _check(lib().ptb_latent_store(_dtype_code(src), _ptr(src), ctypes.c_longlong(src.stride(0)), _ptr(norm_w),
+                                  ctypes.c_float(eps), _ptr(pool), ctypes.byref(batch), _ptr(cos), _ptr(sin), pairs,
+                                  1 if interleaved else 0, rank, rot_dim, _stream(pool)), "latent_store")
+
+
+def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, q_rot_off: int, pool: torch.Tensor, batch: StepBatchC,
+                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, tile_tokens: int, rope, rank: int,
+                     rot_dim: int, scale: float, interleaved: bool = True, n_splits: int = 1) -> torch.Tensor:
+    """Causal attention in latent space. ``q_abs`` [tokens, heads, rank] float32 (queries with the key
+    up-projection folded in), ``q`` [tokens, heads, q_dim] whose entries from ``q_rot_off`` on are the part
+    to rotate, ``pool`` the cache entry's rows [pages, 1, 64, rank + rot_dim]. A tile holds ``tile_tokens``
+    tokens x 16 / tile_tokens heads; ``n_splits`` blocks share a tile's key pages. Returns
+    [tokens, heads, rank] in the model dtype: per head, the softmax-weighted sum of the cached latents."""
+    _need_cuda(q_abs, q, pool, tile_seq, tile_q0)
+    n, heads, q_dim = q.shape
+    if q_abs.dtype != torch.float32 or tuple(q_abs.shape) != (n, heads, rank) or pool.dtype != q.dtype:
+        raise KernelError("latent_attention: q_abs must be float32 [tokens, heads, rank] and the pool of q's dtype")
+    if pool.shape[-1] != rank + rot_dim or q_rot_off + rot_dim > q_dim:
+        raise KernelError("latent_attention: sizes do not fit")
+    heads_per_block = max(1, LATENT_ROWS // tile_tokens)
+    out = torch.empty((n, heads, rank), dtype=q.dtype, device=q.device)
+    cos, sin = rope if rope is not None else (None, None)
+    pairs = 0 if cos is None else cos.shape[1]
+    part = None
+    if n_splits > 1:
+        need = int(lib().ptb_latent_part_floats(n_tiles, heads, heads_per_block, n_splits, rank))
+        part = torch.empty(need, dtype=torch.float32, device=q.device)
+    _check(lib().ptb_latent_attention(_dtype_code(q), _ptr(q_abs), _ptr(q), q_dim, q_rot_off, _ptr(pool), _ptr(part),
+                                      _ptr(out), ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(cos),
+                                      _ptr(sin), pairs, 1 if interleaved else 0, heads, rank, rot_dim, tile_tokens,
+                                      heads_per_block, ctypes.c_float(scale), n_splits, _stream(q)), "latent_attention")
+    if n_splits > 1:
+        global launches
+        launches += 1
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Block-diagonal linear layers and the gated linear recurrence
+def block_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+                 out_dtype: Optional[torch.dtype] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[t, g] = act(w[g] @ x[t, g] + bias[g]) [* sigmoid(gate[t, g])]: ``x`` [tokens, groups, K] (any
+    strides with unit stride along K), ``w`` [groups, N, K], ``bias`` [groups, N] float32, ``gate``
+    [tokens, groups * N] (rows may be wider apart). ``act``: "none" or "sigmoid". Returns
+    [tokens, groups, N] in ``out_dtype`` (float32, or the input's dtype)."""
+    _need_cuda(w, bias)
+    m, g, k = x.shape
+    n = w.shape[1]
+    if x.stride(2) != 1 or tuple(w.shape) != (g, n, k) or w.dtype != x.dtype:
+        raise KernelError("block_linear: shapes or dtypes do not fit")
+    if gate is not None and (gate.stride(1) != 1 or tuple(gate.shape) != (m, g * n) or gate.dtype != x.dtype):
+        raise KernelError("block_linear: the gate does not fit")
+    out_dtype = out_dtype or x.dtype
+    y = torch.empty((m, g, n), dtype=out_dtype, device=x.device)
+    _check(lib().ptb_block_linear(_dtype_code(x), _dtype_code(y), _ptr(x), ctypes.c_longlong(x.stride(0)),
+                                  ctypes.c_longlong(x.stride(1)), _ptr(w), _ptr(bias), _ptr(y), _ptr(gate),
+                                  ctypes.c_longlong(0 if gate is None else gate.stride(0)), m, g, n, k,
+                                  {"none": 0, "sigmoid": 1}[act], _stream(x)), "block_linear")
+    return y
+
+
+def rglru_conv(proj: torch.Tensor, by: torch.Tensor, bx: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor,
+               state: torch.Tensor, slots: torch.Tensor, batch: StepBatchC):
+    """From ``proj`` [tokens, 2 R] (gate branch | recurrent branch, before their biases): the gate branch's
+    gelu_tanh and the recurrent branch's causal convolution over each sequence, earlier inputs from
+    ``state`` (rows by cache slot: [S | last taps - 1 inputs]). Returns (y_act, u), [tokens, R] each."""
+    _need_cuda(proj, by, bx, conv_w, conv_b, slots)
+    n, two_r = proj.shape
+    r = two_r // 2
+    taps = conv_w.shape[1]
+    if state.stride(1) != 1 or state.shape[1] != r * taps or state.dtype != torch.float32:
+        raise KernelError("rglru_conv: the state rows must hold R * taps float32 values")
+    y_act = torch.empty((n, r), dtype=proj.dtype, device=proj.device)
+    u = torch.empty_like(y_act)
+    _check(lib().ptb_rglru_conv(_dtype_code(proj), _ptr(proj), _ptr(by), _ptr(bx), _ptr(conv_w), _ptr(conv_b),
+                                _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(slots), ctypes.byref(batch),
+                                _ptr(y_act), _ptr(u), r, taps, _stream(proj)), "rglru_conv")
+    return y_act, u
+
+
+def rglru_scan(gates: torch.Tensor, u: torch.Tensor, y_act: torch.Tensor, lam: torch.Tensor, proj: torch.Tensor,
+               bx: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, batch: StepBatchC, blocks: int, taps: int,
+               decay: float) -> torch.Tensor:
+    """The recurrence over each sequence's new tokens from and into ``state``; ``gates``
+    [tokens, blocks, 2 * R / blocks] float32 (recurrence gate | input gate, after their sigmoid).
+    Returns (S * y_act) [tokens, R] in the model dtype."""
+    _need_cuda(gates, u, y_act, lam, proj, bx, slots)
+    n, r = u.shape
+    if gates.dtype != torch.float32 or gates.numel() != n * 2 * r or state.stride(1) != 1 or state.shape[1] != r * taps:
+        raise KernelError("rglru_scan: gates or state do not fit")
+    out = torch.empty_like(u)
+    _check(lib().ptb_rglru_scan(_dtype_code(u), _ptr(gates), _ptr(u), _ptr(y_act), _ptr(lam), _ptr(proj), _ptr(bx),
+                                _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(slots), ctypes.byref(batch),
+                                _ptr(out), r, blocks, taps, ctypes.c_float(decay), _stream(u)), "rglru_scan")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Routed experts
+EXPERT_TILE_ROWS = (16, 64)   # rows of a tile of the grouped products: few pairs, many pairs
+
+
+def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, n_groups: int, keep: int, top: int,
+          scale: float):
+    """Router of a mixture of experts, float32: softmax over all outputs, choice by score + correction
+    among the ``keep`` best of ``n_groups`` groups, weights = score * scale. Returns (ids int32
+    [tokens, top], weights float32 [tokens, top])."""
+    _need_cuda(h, w_router, correction)
+    n_tokens, width = h.shape
+    n = w_router.shape[0]
+    if w_router.dtype != torch.float32 or correction.dtype != torch.float32 or w_router.shape[1] != width:
+        raise KernelError("route: the router's matrix and correction are float32 [outputs, width] and [outputs]")
+    ids = torch.empty((n_tokens, top), dtype=torch.int32, device=h.device)
+    gates = torch.empty((n_tokens, top), dtype=torch.float32, device=h.device)
+    _check(lib().ptb_route(_dtype_code(h), _ptr(h), _ptr(w_router), _ptr(correction), _ptr(ids), _ptr(gates), n_tokens,
+                           width, n, n_groups, keep, top, ctypes.c_float(scale), _stream(h)), "route")
+    return ids, gates
+
+
+def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_gate_up: torch.Tensor,
+                   w_down: torch.Tensor, base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """base + sum over a token's choices of weight * expert(h): experts ``w_gate_up`` [E, 2 F, width]
+    (gate rows, then up rows) and ``w_down`` [E, width, F] compute down(silu(gate h) * (up h)); an id >= E
+    is an identity expert. Pairs are sorted by expert on the device and run as tiles of grouped
+    products. Returns [tokens, width] in ``base``'s dtype (float32 without a base)."""
+    _need_cuda(h, ids, gates, w_gate_up, w_down, base)
+    n_tokens, width = h.shape
+    top = ids.shape[1]
+    n_experts, two_f, _ = w_gate_up.shape
+    f = two_f // 2
+    pairs = n_tokens * top
+    tile_rows = EXPERT_TILE_ROWS[0] if pairs <= 8 * n_experts else EXPERT_TILE_ROWS[1]
+    max_tiles = pairs // tile_rows + min(pairs, n_experts)
+    L = lib()
+    plan = torch.empty(int(L.ptb_expert_plan_words(pairs, max_tiles)), dtype=torch.int32, device=h.device)
+    stream = _stream(h)
+    _check(L.ptb_expert_plan(_ptr(ids), _ptr(plan), pairs, n_experts, tile_rows, max_tiles, stream), "expert_plan")
+    code = _dtype_code(h)
+    a = torch.empty((pairs, f), dtype=h.dtype, device=h.device)
+    _check(L.ptb_expert_linear(code, 0, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
+                               tile_rows, stream), "expert_linear (gate, up)")
+    y = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
+    _check(L.ptb_expert_linear(code, 1, _ptr(a), _ptr(w_down), _ptr(y), _ptr(plan), pairs, max_tiles, top, width, f,
+                               tile_rows, stream), "expert_linear (down)")
+    if base is not None and (base.shape != h.shape or base.dtype not in (torch.float32, h.dtype)):
+        raise KernelError("routed_experts: base must have the input's shape, in float32 or the input's dtype")
+    out = torch.empty((n_tokens, width), dtype=torch.float32 if base is None else base.dtype, device=h.device)
+    row_of_pair = plan[1 + 3 * max_tiles:1 + 3 * max_tiles + pairs]
+    _check(L.ptb_expert_combine(code, _dtype_code(out), _ptr(base), _ptr(h), _ptr(y), _ptr(ids), _ptr(gates),
+                                _ptr(row_of_pair), _ptr(out), n_tokens, width, top, stream), "expert_combine")
+    return out

@@ -107,6 +107,9 @@ class ModelSpec:
     embedding_scale: float = 1.0                  # x = table[ids] * embedding_scale
     embedding_norm: Optional[PartSpec] = None     # then a norm of the embeddings
     logit_scale: float = 1.0                      # logits = (rows @ head.T) * logit_scale
+    # the residual stream between the blocks is float32 whatever the model dtype (a bfloat16 model then
+    # rounds only what enters a matrix product); False: the stream has the model dtype
+    stream_float32: bool = False
 
     def resolved_schedule(self) -> List[ScheduleEntry]:
         if self.schedule is not None:
@@ -117,11 +120,14 @@ class ModelSpec:
 @dataclasses.dataclass(frozen=True)
 class CacheNeed:
     """What a mixer wants of the cache for one cache entry. ``kind`` is ``"full"`` (all keys
-    and values of the sequence) or ``"window"`` (the last ``window`` of them)."""
+    and values of the sequence) or ``"window"`` (the last ``window`` of them). ``v_head_dim``: size of a
+    value row if it differs from a key row's; 0 for an entry that keeps one row per token only (a mixer
+    whose values are part of its keys: latent attention)."""
     kind: str
     kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: Optional[int] = None
 
 
 @dataclasses.dataclass(frozen=True)

@@ -5,8 +5,10 @@ output is ``(x + mixer) + ff``, each sum formed in float32 in the epilogue of th
 produces the second term; the reference adds in the order ``x + (ff + mixer)`` (FalconDecoderLayer with parallel attention,
 src/transformers/models/falcon/modeling_falcon.py:630-634, 652-654, 673-676); with a
 ``norm_ff`` child the feed-forward has its own norm of x, else it shares the mixer's.
-``sequential``: ``r = x + mixer(norm(x))``, then ``r + ff(norm_ff(r))`` (:656-659, 676).
-Sums are formed in float32 and rounded once.
+``sequential``: ``r = x + mixer(norm(x))``, then ``r + ff(norm_ff(r))`` (:656-659, 676); without a
+``feed_forward`` child the block ends at ``r``.
+Sums are formed in float32 and rounded once; where the model keeps its residual stream in float32
+(``ModelSpec.stream_float32``) they are not rounded at all.
 """
 from __future__ import annotations
 
@@ -18,7 +20,10 @@ def _plus(kernels, part, base, *args):
     kernel's float32 epilogue; for any other part the sum is a kernel of its own."""
     if getattr(part, "fuses_add", False):
         return part.forward(*args, add=base)
-    return kernels.residual(base, part.forward(*args))
+    y = part.forward(*args)
+    if base.dtype != y.dtype:       # a float32 stream takes a branch's result of the model dtype
+        return kernels.add_stream(base, y)
+    return kernels.residual(base, y)
 
 
 @register_part("block", "parallel")
@@ -86,12 +91,15 @@ class SequentialBlock(Part):
     def __init__(self, build: BuildContext, spec: PartSpec):
         super().__init__(build, spec)
         self.norm_mixer = self.children["norm_mixer"]
-        self.norm_ff = self.children["norm_ff"]
         self.mixer = self.children["mixer"]
-        self.feed_forward = self.children["feed_forward"]
+        # a block without a feed-forward is its mixer's half alone
+        self.feed_forward = self.children.get("feed_forward")
+        self.norm_ff = self.children["norm_ff"] if self.feed_forward is not None else None
 
     def forward(self, x, ctx, entry):
         k = self.build.kernels
         x = resolve(k, x)
         r = _plus(k, self.mixer, x, self.norm_mixer.forward(x), ctx, entry)
+        if self.feed_forward is None:
+            return r
         return _plus(k, self.feed_forward, r, self.norm_ff.forward(r), ctx)

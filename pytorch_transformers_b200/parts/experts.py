@@ -1,0 +1,65 @@
+"""The routed feed-forward: a mixture of small gated feed-forward experts with a group-limited router.
+
+Router, per token and in float32: ``s = softmax(W_r h)`` over all ``experts + identity`` outputs;
+choice scores ``s + correction``; the outputs form ``groups`` equal groups of neighbours, a group's score
+is its largest choice score and only the ``keep`` best groups stay eligible; the ``top`` largest eligible
+choice scores are chosen; a chosen output weighs ``s * scale`` (no renormalisation). Expert e computes
+``W_down (silu(W_gate h) * (W_up h))``; the last ``identity`` outputs are identity experts that pass
+``h`` on and have no tensors. The result is the weighted sum over the chosen, added to the residual
+stream in float32 in the same kernel.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .base import BuildContext, ParamDecl, Part, PartSpec, register_part
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(Part):
+    graph_safe = True
+    fuses_add = True
+
+    def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, inner: int, experts: int, top: int,
+                 identity: int = 0, groups: int = 1, keep: int = 1, scale: float = 1.0):
+        super().__init__(build, spec)
+        self.hidden, self.inner, self.experts, self.top = int(hidden), int(inner), int(experts), int(top)
+        self.identity, self.groups, self.keep, self.scale = int(identity), int(groups), int(keep), float(scale)
+        n = self.experts + self.identity
+        if self.experts <= 0 or self.identity < 0 or self.groups <= 0 or n % self.groups:
+            raise ValueError(f"{n} router outputs do not form {self.groups} equal groups")
+        if not (0 < self.keep <= self.groups) or not (0 < self.top <= n // self.groups * self.keep):
+            raise ValueError(f"cannot choose {self.top} of {n} outputs in {self.keep} of {self.groups} groups")
+        if n > 512:
+            raise ValueError(f"the router kernel takes up to 512 outputs, got {n}")
+        self.p_router = self.p_correction = self.p_gate_up = self.p_down = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        n = self.experts + self.identity
+        d = {"router": ParamDecl((n, self.hidden), role="vector"), "correction": ParamDecl((n,), role="vector")}
+        for e in range(self.experts):
+            d[f"e{e}.gate"] = ParamDecl((self.inner, self.hidden))
+            d[f"e{e}.up"] = ParamDecl((self.inner, self.hidden))
+            d[f"e{e}.down"] = ParamDecl((self.hidden, self.inner))
+        return d
+
+    def bind(self, t: Dict[str, torch.Tensor]) -> None:
+        self.p_router, self.p_correction = t["router"].contiguous(), t["correction"]
+        E, F = self.experts, self.inner
+        # all experts in two tensors for the grouped products: [E, 2 F, hidden] (gate rows, then up rows), [E, hidden, F]
+        gate_up = torch.empty((E, 2 * F, self.hidden), dtype=t["e0.gate"].dtype, device=t["e0.gate"].device)
+        down = torch.empty((E, self.hidden, F), dtype=gate_up.dtype, device=gate_up.device)
+        for e in range(E):
+            gate_up[e, :F] = t.pop(f"e{e}.gate")
+            gate_up[e, F:] = t.pop(f"e{e}.up")
+            down[e] = t.pop(f"e{e}.down")
+        self.p_gate_up, self.p_down = gate_up, down
+
+    def forward(self, x, ctx, add=None):
+        k = self.build.kernels
+        if callable(add):
+            add = add()
+        ids, weights = k.route(x, self.p_router, self.p_correction, self.groups, self.keep, self.top, self.scale)
+        return k.routed_experts(x, ids, weights, self.p_gate_up, self.p_down, base=add)

@@ -29,7 +29,20 @@ def linear(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
     if weight.dtype == torch.float32:
         y = kernels.linear_f32(x, weight, bias, act)
         return y if add is None else kernels.residual(add, y)
+    if x.dtype != weight.dtype:
+        raise ValueError(f"linear: input of {x.dtype} meets a matrix of {weight.dtype}")
     rows, k = x.shape
+    if add is not None and add.dtype == torch.float32:
+        # a float32 residual stream beside bfloat16 matrices: the product leaves its float32 accumulator
+        # unrounded and the sum is formed in float32
+        if bias is None and act == "none":
+            if kernels.skinny_linear_preferred(rows, k, weight.shape[0]):
+                y = kernels.skinny_linear(x, weight, out_dtype=torch.float32)
+            else:
+                y = kernels.matmul_nt(x, weight, out_dtype=torch.float32)
+        else:
+            y = linear(kernels, x, weight, bias, act)
+        return kernels.add_stream(add, y)
     if kernels.skinny_linear_preferred(rows, k, weight.shape[0]):
         return kernels.skinny_linear(x, weight, bias, act, add)
     if TC_LINEAR_ROWS is not None and rows <= TC_LINEAR_ROWS and kernels.tc_linear_takes(rows, k):

@@ -27,12 +27,23 @@ class LayerNorm(Part):
             d["bias"] = ParamDecl((self.size,), role="vector", init="normal")
         return d
 
+    def _stream(self, x) -> bool:
+        """Is ``x`` a float32 residual stream of a model whose matrices are not float32? Its norm is then
+        read in float32 and written in the model dtype."""
+        import torch
+        return x.dtype == torch.float32 and self.build.dtype != torch.float32
+
     def forward(self, x):
+        if self._stream(x):
+            return self.build.kernels.norm_stream(x, self.p_weight, self.p_bias, self.eps, self.kind, self.build.dtype)
         return self.build.kernels.norm(x, self.p_weight, self.p_bias, self.eps, self.kind)
 
     def forward_sum(self, x, addend, other: "LayerNorm" = None):
         """Norm of ``x + addend``: returns (the sum, its norm[, ``other``'s norm of it]) from one kernel."""
         k = self.build.kernels
+        if self._stream(x):
+            total, y = k.norm_stream(x, self.p_weight, self.p_bias, self.eps, self.kind, self.build.dtype, addend=addend)
+            return (total, y) if other is None else (total, y, other.forward(total))
         if other is not None and (other.kind != self.kind or other.eps != self.eps or other.size != self.size):
             total, y = k.norm(x, self.p_weight, self.p_bias, self.eps, self.kind, addend=addend)
             return total, y, other.forward(total)
@@ -43,7 +54,7 @@ class LayerNorm(Part):
 
     def forward_pair(self, x, other: "LayerNorm"):
         """Two norms of the same input with the same statistics: one read, two outputs."""
-        if other.kind != self.kind or other.eps != self.eps or other.size != self.size:
+        if other.kind != self.kind or other.eps != self.eps or other.size != self.size or self._stream(x):
             return self.forward(x), other.forward(x)
         return self.build.kernels.norm(x, self.p_weight, self.p_bias, self.eps, self.kind,
                                        gain2=other.p_weight, bias2=other.p_bias)
