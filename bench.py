@@ -533,7 +533,192 @@ def run_fill(args):
     return 0
 
 
+# ---- Pafevik beside Falcon at equal size (`--only pafevik [--size s|m]`) ----
+# Sizes that resemble a served model's layers: the width, 16 or 32 heads of 96 plain + 32 rotated query/key
+# entries and values of 128, key/value latents of 512, a recurrence 4/3 of the width wide in 16 blocks with 4
+# taps, 64 experts of 1,408 of which a token uses 6 (in 4 of 8 groups). Four layers: latent attention,
+# two recurrent layers, latent attention on the first layer's cache entry. Falcon beside it has the same
+# width, layers, heads (of 128) and a dense feed-forward as wide as the experts a token uses.
+PAFEVIK_SIZES = {"s": dict(width=2048, heads=16, q_rank=768), "m": dict(width=4096, heads=32, q_rank=1536)}
+
+
+def pafevik_config(size):
+    z = PAFEVIK_SIZES[size]
+    w, heads = z["width"], z["heads"]
+    att = {"heads": heads, "dim": 96, "rot_dim": 32, "vdim": 128, "q_rank": z["q_rank"], "kv_rank": 512,
+           "rot": {"base": 10000.0, "dims": 32}, "scale": 128 ** -0.5}
+    rec = {"width": w * 4 // 3 // 256 * 256, "blocks": 16, "conv": 4}
+    mlp = {"kind": "moe", "expert": {"ff": 1408},
+           "router": {"experts": 64, "top": 6, "identity": 0, "scale": 1.0, "groups": {"count": 8, "keep": 4}}}
+    layers = [{"type": "latent_attention", "mixer": dict(att), "mlp": mlp}, {"type": "rglru", "mixer": rec, "mlp": mlp},
+              {"type": "rglru", "mixer": rec, "mlp": mlp},
+              {"type": "latent_attention", "mixer": dict(att, kv_from=0), "mlp": mlp}]
+    return {"architecture": "Pafevik", "vocab": 32000, "width": w, "norm": {"eps": 1e-6}, "logit_scale": 1.0, "layers": layers}
+
+
+def falcon_beside(size):
+    z = PAFEVIK_SIZES[size]
+    return dict(vocab_size=32000, hidden_size=z["width"], num_hidden_layers=4, num_attention_heads=z["heads"],
+                num_kv_heads=z["heads"], new_decoder_architecture=True, num_ln_in_parallel_attn=2,
+                ffn_hidden_size=6 * 1408 * 3 // 2, rope_theta=10000.0, bias=False, alibi=False, layer_norm_epsilon=1e-5,
+                max_position_embeddings=8192, tie_word_embeddings=False, activation="gelu")
+
+
+class KernelTimes:
+    """Times every call of the kernel module's entry points with a pair of CUDA events while it is on."""
+    NAMES = ("gather_rows", "norm", "norm_stream", "add_stream", "residual", "bias_act_", "to_float", "matmul_nt",
+             "skinny_linear", "linear_f32", "rope_table", "split_rotate_store", "attention_tc", "attention_mma",
+             "attention_generic", "attention_decode", "attention_decode_tc", "latent_store", "latent_attention",
+             "latent_expand", "block_linear", "rglru_conv", "rglru_scan", "rglru_scan_chunks", "route", "routed_experts", "scale_")
+
+    def __init__(self, kernels):
+        self.k, self.records, self.saved = kernels, [], {}
+
+    def __enter__(self):
+        import torch
+        for name in self.NAMES:
+            fn = getattr(self.k, name, None)
+            if fn is None:
+                continue
+            self.saved[name] = fn
+
+            def timed(*a, _fn=fn, _name=name, **kw):
+                b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                b.record()
+                out = _fn(*a, **kw)
+                e.record()
+                self.records.append((_name, b, e))
+                return out
+            setattr(self.k, name, timed)
+        return self
+
+    def __exit__(self, *exc):
+        for name, fn in self.saved.items():
+            setattr(self.k, name, fn)
+
+    def table(self):
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for name, b, e in self.records:
+            t = out.setdefault(name, [0, 0.0])
+            t[0] += 1
+            t[1] += b.elapsed_time(e)
+        return {n: {"calls": c, "ms": round(ms, 4)} for n, (c, ms) in sorted(out.items(), key=lambda kv: -kv[1][1])}
+
+
+def run_pafevik(args):
+    import torch
+
+    import pytorch_transformers_b200 as ptb
+    from pytorch_transformers_b200 import kernels
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(0)
+    tokens, batch, context = args.prefill_tokens, args.batch, args.context
+    raw = pafevik_config(args.size)
+    models = {"pafevik": ptb.AutoModelForCausalLM.from_config(ptb.PafevikConfig.from_dict(raw), seed=0, dtype="bfloat16"),
+              "falcon": ptb.AutoModelForCausalLM.from_config(ptb.FalconConfig.from_dict(falcon_beside(args.size)), seed=0,
+                                                             dtype="bfloat16")}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    result = {"only": "pafevik", "size": args.size, "prefill_tokens": tokens, "batch": batch, "context": context,
+              "config": {"width": raw["width"], "layers": len(raw["layers"]), "heads": raw["layers"][0]["mixer"]["heads"]}}
+    for name, model in models.items():
+        vocab = model.spec.vocab_size
+        prompt = torch.randint(0, vocab, (1, tokens), generator=gen).tolist()
+        cache = model.new_cache(max(tokens + 64, batch * ((context + args.steps + args.warmup + 70) // 64 * 64)))
+
+        def prefill_once():
+            s = cache.open()
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            model.step(cache, [s], prompt, want="last")
+            b.record()
+            torch.cuda.synchronize()
+            cache.close(s)
+            return a.elapsed_time(b)
+
+        times = [prefill_once() for _ in range(2 + 3)][2:]
+        with KernelTimes(kernels) as kt:
+            prefill_once()
+        pre_kernels = kt.table()
+        pre_ms = statistics.median(times)
+        # decode: `batch` sequences of `context` tokens, then single tokens
+        slots = [cache.open() for _ in range(batch)]
+        chunk = max(1, 8192 // context)
+        for i in range(0, batch, chunk):
+            ps = torch.randint(0, vocab, (len(slots[i:i + chunk]), context), generator=gen).tolist()
+            model.step(cache, slots[i:i + chunk], ps, want="last")
+        one = [[1]] * batch
+        for _ in range(args.warmup):
+            model.step(cache, slots, one, want="last")
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            model.step(cache, slots, one, want="last")
+        b.record()
+        torch.cuda.synchronize()
+        dec_ms = a.elapsed_time(b) / args.steps
+        graphs, model.use_graphs = model.use_graphs, False
+        with KernelTimes(kernels) as kt:
+            model.step(cache, slots, one, want="last")
+        dec_kernels = kt.table()
+        model.use_graphs = graphs
+        cache.close_all()
+        weights = model.weight_bytes()
+        result[name] = {"prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(tokens / pre_ms * 1e3, 1),
+                        "decode_ms_per_step": round(dec_ms, 4), "decode_tokens_per_s": round(batch / dec_ms * 1e3, 1),
+                        "weight_GB": round(weights / 1e9, 3),
+                        "decode_weight_GBps": round(weights / dec_ms / 1e6, 1),
+                        "prefill_kernels_ms": pre_kernels, "decode_kernels_ms": dec_kernels}
+        del cache
+        torch.cuda.empty_cache()
+    # the new kernels against their rooflines (algorithmic bytes or FLOPs over the measured peaks)
+    m = raw["layers"][0]["mixer"]
+    H, dk, rank = m["heads"], m["kv_rank"] + m["rot_dim"], m["kv_rank"]
+    pairs = tokens * 6
+
+    def per_call(table, key):
+        return table[key]["ms"] / table[key]["calls"] if key in table else None
+
+    P, F = result["pafevik"], result["falcon"]
+    roof = {}
+    t = per_call(P["prefill_kernels_ms"], "latent_attention")
+    if t:
+        roof["latent_attention_prefill_TFLOPs_as_run"] = round(P.get("latent_prefill_flops", H * tokens * (tokens + 1) / 2 * 2 * (dk + rank)) / t / 1e9, 1)
+    t = per_call(F["prefill_kernels_ms"], "attention_tc")
+    if t:
+        roof["falcon_attention_prefill_TFLOPs"] = round(H * tokens * (tokens + 1) / 2 * 4 * 128 / t / 1e9, 1)
+    t = per_call(P["decode_kernels_ms"], "latent_attention")
+    if t:
+        roof["latent_attention_decode_GBps"] = round(batch * context * dk * 2 / t / 1e6, 1)
+    for key in ("attention_decode", "attention_decode_tc"):
+        t = per_call(F["decode_kernels_ms"], key)
+        if t:
+            roof["falcon_" + key + "_GBps"] = round(batch * context * 2 * H * 128 * 2 / t / 1e6, 1)
+    t = per_call(P["prefill_kernels_ms"], "routed_experts")
+    if t:
+        roof["experts_prefill_TFLOPs"] = round(pairs * 3 * 2 * raw["width"] * 1408 / t / 1e9, 1)
+    t = per_call(P["decode_kernels_ms"], "routed_experts")
+    if t:
+        touched = min(64, batch * 6)
+        roof["experts_decode_GBps_at_most"] = round(touched * 3 * raw["width"] * 1408 * 2 / t / 1e6, 1)
+    t = per_call(P["prefill_kernels_ms"], "rglru_scan_chunks")
+    if t:
+        R = raw["layers"][1]["mixer"]["width"]
+        roof["rglru_scan_prefill_GBps"] = round(tokens * R * (8 + 2 + 2 + 2) / t / 1e6, 1)
+    result["roofline"] = roof
+    result["peaks"] = pk
+    print(json.dumps(result))
+    return 0
+
+
 def run_ours(args):
+    if args.only == "pafevik":
+        return run_pafevik(args)
     if args.only == "sample":
         return run_sample(args)
     if args.only == "decode-attention":
@@ -809,9 +994,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "prefill-attention", "config", "linear",
-                             "fill", "mma-cadence"],
+                             "fill", "mma-cadence", "pafevik"],
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
+    ap.add_argument("--size", default="s", choices=sorted(PAFEVIK_SIZES), help="layer sizes for --only pafevik")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per sequence for --only decode")
     ap.add_argument("--past", type=int, default=0, help="cached tokens before the prompt for --only prefill-attention")

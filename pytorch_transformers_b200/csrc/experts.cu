@@ -11,30 +11,40 @@
 namespace {
 
 constexpr int ROUTE_VPL = 16;   // router outputs per lane: up to 512 outputs
-constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_WARPS = 16;
 
+// One block per token. The warps share the outputs' dot products (a warp per output, lanes along the
+// width, a fixed order of sums whatever else is in the batch); warp 0 then scores and chooses.
 template <typename T>
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ correction,
              int* __restrict__ ids, float* __restrict__ gates, int n_tokens, int width, int n, int n_groups, int keep,
              int top, float route_scale) {
-  extern __shared__ float sm[];   // per warp: n choice scores, then n_groups group scores
+  extern __shared__ float sm[];   // n logits, n choice scores, n_groups group scores
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int t = blockIdx.x * ROUTE_WARPS + warp;
-  if (t >= n_tokens) return;
-  float* choice = sm + size_t(warp) * (n + n_groups);
+  const int t = blockIdx.x;
+  float* zs = sm;
+  float* choice = zs + n;
   float* gscore = choice + n;
   const T* x = h + size_t(t) * width;
-  float z[ROUTE_VPL], s[ROUTE_VPL];
-  float zmax = -INFINITY;
-  for (int e = 0; e < n; ++e) {
+  for (int e = warp; e < n; e += ROUTE_WARPS) {
     const float* wr = w_router + size_t(e) * width;
     float d = 0.f;
     for (int k = lane; k < width; k += 32) d = fmaf(wr[k], to_f(x[k]), d);
     d = warp_sum(d);
-    if (e % 32 == lane) z[e / 32] = d;
-    zmax = fmaxf(zmax, d);
+    if (lane == 0) zs[e] = d;
   }
+  __syncthreads();
+  if (warp != 0) return;
+  float z[ROUTE_VPL], s[ROUTE_VPL];
+  float zmax = -INFINITY;
+#pragma unroll
+  for (int v = 0; v < ROUTE_VPL; ++v) {
+    const int e = lane + 32 * v;
+    z[v] = (e < n) ? zs[e] : -INFINITY;
+    zmax = fmaxf(zmax, z[v]);
+  }
+  zmax = warp_max(zmax);
   float sum = 0.f;
 #pragma unroll
   for (int v = 0; v < ROUTE_VPL; ++v) {
@@ -295,8 +305,8 @@ PTB_API int ptb_route(int dtype, const void* h, const float* w_router, const flo
   if (n <= 0 || n > 32 * ROUTE_VPL || n_groups <= 0 || n % n_groups != 0 || keep <= 0 || keep > n_groups || top <= 0 ||
       top > (n / n_groups) * keep || width <= 0)
     return PTB_ERR_SIZE;
-  const size_t smem = size_t(ROUTE_WARPS) * (n + n_groups) * sizeof(float);
-  const int grid = (n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
+  const size_t smem = size_t(2 * n + n_groups) * sizeof(float);
+  const int grid = n_tokens;
   if (dtype == PTB_F32)
     route_kernel<float><<<grid, 32 * ROUTE_WARPS, smem, stream>>>((const float*)h, w_router, correction, ids, gates,
                                                                   n_tokens, width, n, n_groups, keep, top, route_scale);

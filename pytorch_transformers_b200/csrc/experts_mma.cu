@@ -1,0 +1,162 @@
+// The experts' grouped matrix products in bfloat16 on the tensor cores (mma.m16n8k16, float32 sums):
+// the tiles of the plan that expert_plan_kernel makes (csrc/experts.cu), 64 sorted rows of one expert
+// each. A block of 4 warps takes one tile x 128 rows of the expert's matrix; a warp owns 32 rows of the
+// tile and 64 of the 128 matrix rows. Operands come through a three-stage cp.async ring of [rows][32] tiles whose
+// 16-byte chunks are XOR-swizzled so that ldmatrix meets no bank twice.
+//   mode 0: x rows are gathered from h by token; the 128 matrix rows are 64 gate rows and the 64 up rows
+//           of the same columns; out[row, f] = silu(gate) * up, bfloat16.
+//   mode 1: x rows are the sorted rows themselves; out[row, n] float32.
+// A row's sums do not depend on its place in a tile or on the other rows.
+#include "mma_common.cuh"
+
+namespace {
+
+constexpr int GM = 64, GB = 128, GK = 32, STAGES = 3, GTHREADS = 128;
+
+// byte offset of 16-byte chunk c (0..3) of row r in a [rows][32] bfloat16 tile
+__device__ __forceinline__ uint32_t gswz(int r, int c) { return uint32_t(r * 64 + ((c ^ ((r >> 1) & 3)) << 4)); }
+
+template <int MODE>
+__global__ void __launch_bounds__(GTHREADS)
+expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ out_v,
+                         const int* __restrict__ plan, int pairs, int max_tiles, int top, int N, int K) {
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int expert = plan[1 + tile], row0 = plan[1 + max_tiles + tile], rows = plan[1 + 2 * max_tiles + tile];
+  const int* pair_of_row = plan + 1 + 3 * max_tiles + pairs;
+  __shared__ __align__(128) unsigned char a_s[STAGES][GM * 64];
+  __shared__ __align__(128) unsigned char b_s[STAGES][GB * 64];
+  __shared__ int src_row[GM];
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  constexpr int NOUT = MODE == 0 ? 64 : 128;     // output columns of a block
+  const int n0 = blockIdx.x * NOUT;
+  if (tid < GM) src_row[tid] = (tid < rows) ? (MODE == 0 ? pair_of_row[row0 + tid] / top : row0 + tid) : -1;
+  __syncthreads();
+  const __nv_bfloat16* we = w + size_t(expert) * (MODE == 0 ? 2 : 1) * N * K;
+
+  auto load_stage = [&](int stage, int k0) {
+    // A: 64 rows x 4 chunks; B: 128 rows x 4 chunks
+    for (int i = tid; i < GM * 4; i += GTHREADS) {
+      const int r = i / 4, c = i % 4, k = k0 + c * 8;
+      const uint32_t dst = smem_u32(a_s[stage]) + gswz(r, c);
+      const int sr = src_row[r];
+      if (sr >= 0 && k < K) cp_async16(dst, x + size_t(sr) * K + k);
+      else *reinterpret_cast<uint4*>(a_s[stage] + gswz(r, c)) = make_uint4(0, 0, 0, 0);
+    }
+    for (int i = tid; i < GB * 4; i += GTHREADS) {
+      const int r = i / 4, c = i % 4, k = k0 + c * 8;
+      const uint32_t dst = smem_u32(b_s[stage]) + gswz(r, c);
+      // row of the expert's matrix. mode 0: staged rows 64 nh + 32 part + cc hold column n0 + 32 nh + cc of the gate
+      // (part 0) or up (part 1) rows, so that a warp (one nh) has both for its 32 columns
+      int gn, col;
+      if (MODE == 0) {
+        col = n0 + (r >> 6) * 32 + (r & 31);
+        gn = ((r >> 5) & 1) ? N + col : col;
+      } else {
+        col = gn = n0 + r;
+      }
+      const bool ok = col < N && k < K;
+      if (ok) cp_async16(dst, we + size_t(gn) * K + k);
+      else *reinterpret_cast<uint4*>(b_s[stage] + gswz(r, c)) = make_uint4(0, 0, 0, 0);
+    }
+  };
+
+  const int wm = warp >> 1, wn = warp & 1;     // this warp: rows 32 wm .. + 31, staged matrix rows 64 wn .. + 63
+  float acc[2][8][4];
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[mi][j][q] = 0.f;
+
+  const int k_tiles = (K + GK - 1) / GK;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < k_tiles) load_stage(s, s * GK);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();   // stage kt has landed for everybody, and stage kt - 1 is no longer read
+    const int nxt = kt + STAGES - 1;
+    if (nxt < k_tiles) load_stage(nxt % STAGES, nxt * GK);
+    cp_async_commit();
+    const int st = kt % STAGES;
+    const uint32_t a_base = smem_u32(a_s[st]), b_base = smem_u32(b_s[st]);
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+        ldmatrix_x4(a[mi][0], a[mi][1], a[mi][2], a[mi][3],
+                    a_base + gswz(wm * 32 + mi * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {     // two fragments of 8 columns at a time
+        uint32_t b0, b1, b2, b3;
+        const int id = lane >> 3;
+        ldmatrix_x4(b0, b1, b2, b3, b_base + gswz(wn * 64 + jp * 16 + (id >> 1) * 8 + (lane & 7), ks * 2 + (id & 1)));
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+          mma_bf16(acc[mi][2 * jp], a[mi], b0, b1);
+          mma_bf16(acc[mi][2 * jp + 1], a[mi], b2, b3);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  const int c0 = (lane % 4) * 2;
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 32 + mi * 16 + half * 8 + lane / 4;
+      if (r >= rows) continue;
+      if (MODE == 0) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_v) + size_t(row0 + r) * N;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int col = n0 + wn * 32 + j * 8 + c0 + q;
+            if (col >= N) continue;
+            const float g = acc[mi][j][half * 2 + q], u = acc[mi][j + 4][half * 2 + q];
+            o[col] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+          }
+        }
+      } else {
+        float* o = reinterpret_cast<float*>(out_v) + size_t(row0 + r) * N;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int col = n0 + wn * 64 + j * 8 + c0 + q;
+            if (col < N) o[col] = acc[mi][j][half * 2 + q];
+          }
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+// rows of a tile that this kernel takes (the plan must be made with it)
+PTB_API int ptb_expert_linear_mma_tile_rows() { return GM; }
+
+PTB_API int ptb_expert_linear_mma(int mode, const void* x, const void* w, void* out, const int* plan, int pairs,
+                                  int max_tiles, int top, int N, int K, cudaStream_t stream) {
+  if (pairs <= 0 || max_tiles <= 0) return PTB_OK;
+  if (N <= 0 || K <= 0 || K % 8 != 0 || max_tiles > 65535 || top <= 0) return PTB_ERR_SIZE;
+  if (!aligned16(x) || !aligned16(w)) return PTB_ERR_ALIGN;
+  if (mode == 0) {
+    dim3 grid((N + 63) / 64, max_tiles);
+    expert_linear_mma_kernel<0><<<grid, GTHREADS, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, plan,
+                                                               pairs, max_tiles, top, N, K);
+  } else {
+    dim3 grid((N + 127) / 128, max_tiles);
+    expert_linear_mma_kernel<1><<<grid, GTHREADS, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, plan,
+                                                               pairs, max_tiles, top, N, K);
+  }
+  return launch_status();
+}

@@ -222,30 +222,40 @@ latent_attention_kernel(const float* __restrict__ q_abs, const T* __restrict__ q
   }
 }
 
-// merges the splits of a tile in ascending order of their pages
+// merges the splits of a tile in ascending order of their pages: one block per (tile, head chunk, row)
 template <typename T>
 __global__ void latent_join_kernel(const float* __restrict__ part, T* __restrict__ out, StepBatch sb,
                                    const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int heads,
                                    int rank, int tile_tokens, int heads_per_block, int n_splits) {
-  const int tile = blockIdx.x, h0 = blockIdx.y * heads_per_block;
+  extern __shared__ float jw[];   // the splits' weights exp(m_s - m) / l
+  const int tile = blockIdx.x, h0 = blockIdx.y * heads_per_block, r = blockIdx.z;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
   const int toks = min(tile_tokens, sb.seq_new[seq] - q0), start = sb.seq_start[seq];
-  const float* base = part + (size_t(tile) * gridDim.y + blockIdx.y) * n_splits * ROWS * size_t(rank + 2);
-  for (int i = threadIdx.x; i < ROWS * rank; i += blockDim.x) {
-    const int r = i / rank, e = i % rank;
-    const int ti = r / heads_per_block, hh = h0 + r % heads_per_block;
-    if (!(ti < toks && hh < heads && r < tile_tokens * heads_per_block)) continue;
+  const int ti = r / heads_per_block, hh = h0 + r % heads_per_block;
+  if (!(ti < toks && hh < heads && r < tile_tokens * heads_per_block)) return;
+  const float* base = part + (size_t(tile) * gridDim.y + blockIdx.y) * n_splits * ROWS * size_t(rank + 2) + size_t(r) * (rank + 2);
+  const size_t split_stride = size_t(ROWS) * (rank + 2);
+  if (threadIdx.x < 32) {
     float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, base[(size_t(s) * ROWS + r) * (rank + 2)]);
-    float l = 0.f, o = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float* p = base + (size_t(s) * ROWS + r) * (rank + 2);
-      if (p[0] == -INFINITY) continue;
-      const float w = expf(p[0] - m);
-      l += p[1] * w;
-      o += p[2 + e] * w;
+    for (int s = threadIdx.x; s < n_splits; s += 32) m = fmaxf(m, base[s * split_stride]);
+    m = warp_max(m);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; ++s) {      // ascending order, the same in every lane
+      const float ms = base[s * split_stride];
+      const float w = (ms == -INFINITY) ? 0.f : expf(ms - m);
+      l += base[s * split_stride + 1] * w;
+      if (threadIdx.x == 0) jw[s] = w;
     }
-    out[(size_t(start + q0 + ti) * heads + hh) * rank + e] = from_f<T>(l > 0.f ? o / l : 0.f);
+    __syncwarp();
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int s = threadIdx.x; s < n_splits; s += 32) jw[s] *= inv;
+  }
+  __syncthreads();
+  T* o = out + (size_t(start + q0 + ti) * heads + hh) * rank;
+  for (int e = threadIdx.x; e < rank; e += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < n_splits; ++s) v = fmaf(base[s * split_stride + 2 + e], jw[s], v);
+    o[e] = from_f<T>(v);
   }
 }
 
@@ -271,8 +281,8 @@ int launch_latent(const float* q_abs, const void* q, int q_dim, int q_rot_off, c
       rot_pairs, interleaved, heads, rank, rot_dim, tile_tokens, heads_per_block, scale, n_splits);
   int rc = launch_status();
   if (rc != PTB_OK || n_splits <= 1) return rc;
-  latent_join_kernel<T><<<dim3(n_tiles, chunks), 256, 0, stream>>>(part, (T*)out, sb, tile_seq, tile_q0, heads, rank,
-                                                                  tile_tokens, heads_per_block, n_splits);
+  latent_join_kernel<T><<<dim3(n_tiles, chunks, ROWS), 128, n_splits * sizeof(float), stream>>>(
+      part, (T*)out, sb, tile_seq, tile_q0, heads, rank, tile_tokens, heads_per_block, n_splits);
   return launch_status();
 }
 
@@ -344,4 +354,292 @@ PTB_API int ptb_latent_attention(int dtype, const float* q_abs, const void* q, i
                                           rope_cos, rope_sin, rot_pairs, interleaved, heads, rank, rot_dim,
                                           tile_tokens, heads_per_block, scale, n_splits, stream);
   return PTB_ERR_DTYPE;
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same attention in bfloat16 on the tensor cores (mma.m16n8k16, float32 sums), for rank a multiple
+// of 64 and rot_dim a multiple of 16. A block of 4 warps takes the 16 rows of a tile (the heads of a
+// token in a step of single tokens) and walks its share of the key pages. A page [64][rank + rot_dim]
+// comes into shared memory once (cp.async, rows 16 bytes apart from a multiple of 128 so that ldmatrix
+// meets no bank twice) and serves both products: warp w forms the scores of keys 16 w .. 16 w + 15
+// (S = Q K^T over all rank + rot_dim entries), the warps exchange row maxima and sums through shared
+// memory, the weights go to shared memory as bfloat16, and warp w adds P V for the columns
+// w rank / 4 .. (w + 1) rank / 4 of the output, V being the first `rank` entries of the same rows.
+// The query rows are rounded to bfloat16 once (q_abs comes in float32); scores, maxima, sums and the
+// output sums are float32. Splits and their join are those of the general kernel.
+#include "mma_common.cuh"
+
+namespace {
+
+constexpr int MTHREADS = 128;
+
+template <int NF>   // 8-column fragments of the output per warp: rank = 32 NF
+__global__ void __launch_bounds__(MTHREADS)
+latent_attention_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ q, int q_dim,
+                            int q_rot_off, const __nv_bfloat16* __restrict__ pool, float* __restrict__ part,
+                            __nv_bfloat16* __restrict__ out, StepBatch sb, const int* __restrict__ tile_seq,
+                            const int* __restrict__ tile_q0, const float* __restrict__ rope_cos,
+                            const float* __restrict__ rope_sin, int rot_pairs, int interleaved, int heads, int rank,
+                            int rot_dim, int tile_tokens, int heads_per_block, float scale, int n_splits) {
+  extern __shared__ __align__(128) unsigned char msm[];
+  const int dk = rank + rot_dim;
+  const int rowb = dk * 2 + 16;                       // bytes of a staged row
+  unsigned char* q_s = msm;                           // [16][rowb]
+  unsigned char* k_s = q_s + 16 * rowb;               // [64][rowb]
+  unsigned char* p_s = k_s + PTB_PAGE * rowb;         // [16][144]: 64 weights and 16 bytes of padding
+  float* wmax = reinterpret_cast<float*>(p_s + 16 * 144);   // [4][16]
+  float* wsum = wmax + 64;                                  // [4][16]
+
+  const int tile = blockIdx.x, h0 = blockIdx.y * heads_per_block, split = blockIdx.z;
+  const int seq = tile_seq[tile], q0 = tile_q0[tile];
+  const int n_new = sb.seq_new[seq], past = sb.seq_past[seq], start = sb.seq_start[seq];
+  const int toks = min(tile_tokens, n_new - q0);
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int used_rows = tile_tokens * heads_per_block;
+
+  // the query rows, rounded to bfloat16: [q_abs | rotated part]
+  for (int i = tid; i < ROWS * rank; i += MTHREADS) {
+    const int rr = i / rank, e = i % rank;
+    const int ti = rr / heads_per_block, hh = h0 + rr % heads_per_block;
+    const bool ok = ti < toks && hh < heads && rr < used_rows;
+    const float v = ok ? q_abs[(size_t(start + q0 + ti) * heads + hh) * rank + e] : 0.f;
+    reinterpret_cast<__nv_bfloat16*>(q_s + rr * rowb)[e] = __float2bfloat16_rn(v);
+  }
+  const int items = rot_pairs + (rot_dim - 2 * rot_pairs);
+  for (int i = tid; i < ROWS * items; i += MTHREADS) {
+    const int rr = i / items, e = i % items;
+    const int ti = rr / heads_per_block, hh = h0 + rr % heads_per_block;
+    const bool ok = ti < toks && hh < heads && rr < used_rows;
+    const size_t tok = size_t(start + q0 + ti);
+    const __nv_bfloat16* src = q + (tok * heads + hh) * q_dim + q_rot_off;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(q_s + rr * rowb) + rank;
+    if (e < rot_pairs) {
+      const int ia = interleaved ? 2 * e : e, ib = interleaved ? 2 * e + 1 : e + rot_pairs;
+      float a = 0.f, b = 0.f;
+      if (ok) rotate_pair(to_f(src[ia]), to_f(src[ib]), rope_cos[tok * rot_pairs + e], rope_sin[tok * rot_pairs + e], a, b);
+      dst[ia] = __float2bfloat16_rn(a);
+      dst[ib] = __float2bfloat16_rn(b);
+    } else {
+      const int j = 2 * rot_pairs + (e - rot_pairs);
+      dst[j] = ok ? src[j] : __float2bfloat16_rn(0.f);
+    }
+  }
+
+  // this thread's two rows of the 16 (accumulator layout of mma.m16n8k16)
+  const int r_lo = lane / 4, r_hi = r_lo + 8;
+  int pos_of[2];
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int rr = hf ? r_hi : r_lo;
+    const int ti = rr / heads_per_block, hh = h0 + rr % heads_per_block;
+    pos_of[hf] = (ti < toks && hh < heads && rr < used_rows) ? past + q0 + ti : -1;
+  }
+  float acc[NF][4];
+#pragma unroll
+  for (int j = 0; j < NF; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  const int last_pos = past + q0 + toks - 1;
+  const int n_blocks = last_pos / PTB_PAGE + 1;
+  const int per = (n_blocks + n_splits - 1) / n_splits;
+  const int kb_lo = split * per, kb_hi = min(n_blocks, kb_lo + per) - 1;
+  const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
+  const int chunks = dk / 8;
+  const uint32_t q_base = smem_u32(q_s), k_base = smem_u32(k_s), p_base = smem_u32(p_s);
+  const int col0 = warp * NF * 8;       // first output column of this warp
+
+  for (int kb = kb_lo; kb <= kb_hi; ++kb) {
+    const __nv_bfloat16* kp = pool + kv_offset(pages[kb], 0, 0, 1, dk);
+    __syncthreads();   // the page before is no longer read (and the query rows are written)
+    for (int i = tid; i < PTB_PAGE * chunks; i += MTHREADS) {
+      const int j = i / chunks, c = i % chunks;
+      cp_async16(k_base + j * rowb + c * 16, kp + size_t(j) * dk + c * 8);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    // scores of keys 16 warp .. 16 warp + 15
+    float s[2][4];
+#pragma unroll
+    for (int f = 0; f < 2; ++f)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[f][c] = 0.f;
+    for (int ks = 0; ks < dk / 16; ++ks) {
+      uint32_t a[4], b0, b1, b2, b3;
+      ldmatrix_x4(a[0], a[1], a[2], a[3], q_base + (lane & 15) * rowb + (ks * 2 + (lane >> 4)) * 16);
+      const int id = lane >> 3;
+      ldmatrix_x4(b0, b1, b2, b3, k_base + (warp * 16 + (id >> 1) * 8 + (lane & 7)) * rowb + (ks * 2 + (id & 1)) * 16);
+      mma_bf16(s[0], a, b0, b1);
+      mma_bf16(s[1], a, b2, b3);
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int f = 0; f < 2; ++f)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key_pos = kb * PTB_PAGE + warp * 16 + f * 8 + (lane % 4) * 2 + (c & 1);
+        const int hf = c >> 1;
+        s[f][c] = (key_pos <= pos_of[hf]) ? s[f][c] * scale : -INFINITY;
+        mx[hf] = fmaxf(mx[hf], s[f][c]);
+      }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
+      mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
+    }
+    if (lane % 4 == 0) {
+      wmax[warp * 16 + r_lo] = mx[0];
+      wmax[warp * 16 + r_hi] = mx[1];
+    }
+    __syncthreads();
+    float corr[2], m_new[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int rr = hf ? r_hi : r_lo;
+      const float mb = fmaxf(fmaxf(wmax[rr], wmax[16 + rr]), fmaxf(wmax[32 + rr], wmax[48 + rr]));
+      m_new[hf] = fmaxf(m_run[hf], mb);
+      corr[hf] = (m_run[hf] == -INFINITY) ? 0.f : expf(m_run[hf] - m_new[hf]);     // m_new = -inf: nothing seen, sums stay 0
+      if (m_new[hf] == -INFINITY) corr[hf] = 1.f;
+    }
+#pragma unroll
+    for (int f = 0; f < 2; ++f)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const float p0 = (s[f][hf * 2] == -INFINITY) ? 0.f : expf(s[f][hf * 2] - m_new[hf]);
+        const float p1 = (s[f][hf * 2 + 1] == -INFINITY) ? 0.f : expf(s[f][hf * 2 + 1] - m_new[hf]);
+        // the weights as the second product sees them, and their sum from the same rounded values
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+        sum[hf] += __bfloat162float(pr.x) + __bfloat162float(pr.y);
+        const int rr = hf ? r_hi : r_lo;
+        *reinterpret_cast<__nv_bfloat162*>(p_s + rr * 144 + (warp * 16 + f * 8 + (lane % 4) * 2) * 2) = pr;
+      }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      sum[hf] += __shfl_xor_sync(0xffffffffu, sum[hf], 1);
+      sum[hf] += __shfl_xor_sync(0xffffffffu, sum[hf], 2);
+    }
+    if (lane % 4 == 0) {
+      wsum[warp * 16 + r_lo] = sum[0];
+      wsum[warp * 16 + r_hi] = sum[1];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int rr = hf ? r_hi : r_lo;
+      l_run[hf] = l_run[hf] * corr[hf] + ((wsum[rr] + wsum[16 + rr]) + (wsum[32 + rr] + wsum[48 + rr]));
+      m_run[hf] = m_new[hf];
+    }
+#pragma unroll
+    for (int j = 0; j < NF; ++j) {
+      acc[j][0] *= corr[0];
+      acc[j][1] *= corr[0];
+      acc[j][2] *= corr[1];
+      acc[j][3] *= corr[1];
+    }
+    // O += P V for this warp's columns
+#pragma unroll
+    for (int ks = 0; ks < PTB_PAGE / 16; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(a[0], a[1], a[2], a[3], p_base + (lane & 15) * 144 + (ks * 2 + (lane >> 4)) * 16);
+      const int id = lane >> 3;
+#pragma unroll
+      for (int jp = 0; jp < NF / 2; ++jp) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3,
+                          k_base + (ks * 16 + (id & 1) * 8 + (lane & 7)) * rowb + (col0 + jp * 16 + (id >> 1) * 8) * 2);
+        mma_bf16(acc[2 * jp], a, b0, b1);
+        mma_bf16(acc[2 * jp + 1], a, b2, b3);
+      }
+    }
+  }
+  const int c0 = (lane % 4) * 2;
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const int rr = hf ? r_hi : r_lo;
+    if (n_splits > 1) {
+      float* p = part + ((size_t(tile) * gridDim.y + blockIdx.y) * n_splits + split) * ROWS * size_t(rank + 2) +
+                 size_t(rr) * (rank + 2);
+      if (warp == 0 && lane % 4 == 0) {
+        p[0] = m_run[hf];
+        p[1] = l_run[hf];
+      }
+#pragma unroll
+      for (int j = 0; j < NF; ++j) {
+        p[2 + col0 + j * 8 + c0] = acc[j][hf * 2];
+        p[2 + col0 + j * 8 + c0 + 1] = acc[j][hf * 2 + 1];
+      }
+    } else if (pos_of[hf] >= 0) {
+      const int ti = rr / heads_per_block, hh = h0 + rr % heads_per_block;
+      const float inv = l_run[hf] > 0.f ? 1.f / l_run[hf] : 0.f;
+      __nv_bfloat16* o = out + (size_t(start + q0 + ti) * heads + hh) * rank + col0;
+#pragma unroll
+      for (int j = 0; j < NF; ++j)
+        *reinterpret_cast<__nv_bfloat162*>(o + j * 8 + c0) = __floats2bfloat162_rn(acc[j][hf * 2] * inv, acc[j][hf * 2 + 1] * inv);
+    }
+  }
+}
+
+template <int NF>
+int launch_latent_mma(const float* q_abs, const void* q, int q_dim, int q_rot_off, const void* pool, float* part,
+                      void* out, const StepBatch& sb, const int* tile_seq, const int* tile_q0, int n_tiles,
+                      const float* rope_cos, const float* rope_sin, int rot_pairs, int interleaved, int heads, int rank,
+                      int rot_dim, int tile_tokens, int heads_per_block, float scale, int n_splits, cudaStream_t stream) {
+  const int rowb = (rank + rot_dim) * 2 + 16;
+  const size_t smem = size_t(16 + PTB_PAGE) * rowb + 16 * 144 + 2 * 64 * sizeof(float);
+  if (smem > 220 * 1024) return PTB_ERR_SIZE;
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(latent_attention_mma_kernel<NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+        cudaSuccess)
+      return PTB_ERR_LAUNCH;
+    configured = smem;
+  }
+  const int chunks = (heads + heads_per_block - 1) / heads_per_block;
+  latent_attention_mma_kernel<NF><<<dim3(n_tiles, chunks, n_splits), MTHREADS, smem, stream>>>(
+      q_abs, (const __nv_bfloat16*)q, q_dim, q_rot_off, (const __nv_bfloat16*)pool, part, (__nv_bfloat16*)out, sb,
+      tile_seq, tile_q0, rope_cos, rope_sin, rot_pairs, interleaved, heads, rank, rot_dim, tile_tokens, heads_per_block,
+      scale, n_splits);
+  int rc = launch_status();
+  if (rc != PTB_OK || n_splits <= 1) return rc;
+  latent_join_kernel<__nv_bfloat16><<<dim3(n_tiles, chunks, ROWS), 128, n_splits * sizeof(float), stream>>>(
+      part, (__nv_bfloat16*)out, sb, tile_seq, tile_q0, heads, rank, tile_tokens, heads_per_block, n_splits);
+  return launch_status();
+}
+
+}  // namespace
+
+PTB_API int ptb_latent_attention_mma_supports(int rank, int rot_dim) {
+  return rank > 0 && rank <= 512 && rank % 64 == 0 && rot_dim >= 0 && rot_dim % 16 == 0;
+}
+
+PTB_API int ptb_latent_attention_mma(const float* q_abs, const void* q, int q_dim, int q_rot_off, const void* pool,
+                                     float* part, void* out, const StepBatch* sb, const int* tile_seq,
+                                     const int* tile_q0, int n_tiles, const float* rope_cos, const float* rope_sin,
+                                     int rot_pairs, int interleaved, int heads, int rank, int rot_dim, int tile_tokens,
+                                     int heads_per_block, float scale, int n_splits, cudaStream_t stream) {
+  if (n_tiles <= 0) return PTB_OK;
+  if (!ptb_latent_attention_mma_supports(rank, rot_dim) || heads <= 0 || rot_pairs < 0 || 2 * rot_pairs > rot_dim ||
+      tile_tokens <= 0 || heads_per_block <= 0 || tile_tokens * heads_per_block > ROWS || n_splits < 1 ||
+      n_splits > 65535 || (heads + heads_per_block - 1) / heads_per_block > 65535)
+    return PTB_ERR_SIZE;
+  if (n_splits > 1 && part == nullptr) return PTB_ERR_SIZE;
+  if (rot_pairs > 0 && (rope_cos == nullptr || rope_sin == nullptr)) return PTB_ERR_SIZE;
+  if (!aligned16(pool) || !aligned16(out)) return PTB_ERR_ALIGN;
+#define PTB_LMMA(NFV)                                                                                               \
+  return launch_latent_mma<NFV>(q_abs, q, q_dim, q_rot_off, pool, part, out, *sb, tile_seq, tile_q0, n_tiles, rope_cos, \
+                                rope_sin, rot_pairs, interleaved, heads, rank, rot_dim, tile_tokens, heads_per_block,   \
+                                scale, n_splits, stream)
+  switch (rank / 64) {
+    case 1: PTB_LMMA(2);
+    case 2: PTB_LMMA(4);
+    case 3: PTB_LMMA(6);
+    case 4: PTB_LMMA(8);
+    case 5: PTB_LMMA(10);
+    case 6: PTB_LMMA(12);
+    case 7: PTB_LMMA(14);
+    default: PTB_LMMA(16);
+  }
+#undef PTB_LMMA
 }

@@ -80,6 +80,84 @@ __global__ void rglru_scan_kernel(const float* __restrict__ gates, const T* __re
   for (int k = 0; k < taps - 1; ++k) st[R + size_t(k) * R + c] = keep[k];
 }
 
+// The same recurrence for long prompts, cut into chunks of consecutive tokens of one sequence so that the
+// chunks run side by side: S_end = A S_start + B with A the product of a chunk's decays and B its result
+// from S_start = 0. Pass 1 (a thread per chunk and channel) finds (A, B) of every chunk; pass 2 (a thread
+// per sequence and channel) walks a sequence's chunks in order, notes every chunk's S_start, and leaves
+// the state (S and the convolution's last inputs); pass 3 (a thread per chunk and channel) runs the
+// chunk again from its S_start and writes the outputs. PASS selects the pass.
+template <typename T, int PASS>
+__global__ void rglru_chunk_kernel(const float* __restrict__ gates, const T* __restrict__ u, const T* __restrict__ y_act,
+                                   const float* __restrict__ lam, const T* __restrict__ proj,
+                                   const float* __restrict__ bx, float* __restrict__ state, long long state_stride,
+                                   const int* __restrict__ slots, StepBatch sb, const int* __restrict__ chunk_seq,
+                                   const int* __restrict__ chunk_q0, const int* __restrict__ seq_chunk0, int n_chunks,
+                                   int chunk_len, float* __restrict__ agg_a, float* __restrict__ agg_b,
+                                   float* __restrict__ s_start, T* __restrict__ out, int R, int bw, int taps,
+                                   float c_decay) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= R) return;
+  if (PASS == 2) {
+    const int seq = blockIdx.y;
+    const int n_new = sb.seq_new[seq], start = sb.seq_start[seq];
+    float* st = state + size_t(slots[seq]) * state_stride;
+    float S = st[c];
+    const int first = seq_chunk0[seq], count = (n_new + chunk_len - 1) / chunk_len;
+    for (int k = first; k < first + count; ++k) {
+      s_start[size_t(k) * R + c] = S;
+      S = fmaf(agg_a[size_t(k) * R + c], S, agg_b[size_t(k) * R + c]);
+    }
+    st[c] = S;
+    float keep[MAX_TAPS];
+    for (int k = 0; k < taps - 1; ++k) {
+      const int jj = n_new - (taps - 1) + k;
+      keep[k] = (jj >= 0) ? to_f(proj[size_t(start + jj) * 2 * R + R + c]) + bx[c] : st[R + size_t(jj + taps - 1) * R + c];
+    }
+    for (int k = 0; k < taps - 1; ++k) st[R + size_t(k) * R + c] = keep[k];
+    return;
+  }
+  const int chunk = blockIdx.y;
+  const int seq = chunk_seq[chunk], q0 = chunk_q0[chunk];
+  const int first = sb.seq_start[seq] + q0, count = min(chunk_len, sb.seq_new[seq] - q0);
+  const float l = lam[c];
+  const float sp = (l > 20.f) ? l : log1pf(expf(l));
+  const size_t goff = size_t(c / bw) * 2 * bw + c % bw;
+  float S = (PASS == 3) ? s_start[size_t(chunk) * R + c] : 0.f, A = 1.f;
+  for (int i = 0; i < count; ++i) {
+    const size_t t = size_t(first + i);
+    const float r = gates[t * 2 * R + goff], in = gates[t * 2 * R + goff + bw];
+    const float log_a = -c_decay * r * sp;
+    const float a = expf(log_a);
+    S = fmaf(a, S, sqrtf(-expm1f(2.f * log_a)) * (in * to_f(u[t * R + c])));
+    if (PASS == 1) A *= a;
+    if (PASS == 3) out[t * R + c] = from_f<T>(S * to_f(y_act[t * R + c]));
+  }
+  if (PASS == 1) {
+    agg_a[size_t(chunk) * R + c] = A;
+    agg_b[size_t(chunk) * R + c] = S;
+  }
+}
+
+template <typename T>
+int launch_rglru_chunks(const float* gates, const void* u, const void* y_act, const float* lam, const void* proj,
+                        const float* bx, float* state, long long state_stride, const int* slots, const StepBatch& sb,
+                        const int* chunk_seq, const int* chunk_q0, const int* seq_chunk0, int n_chunks, int chunk_len,
+                        float* work, void* out, int R, int bw, int taps, float c_decay, cudaStream_t stream) {
+  float* agg_a = work;
+  float* agg_b = work + size_t(n_chunks) * R;
+  float* s_start = work + 2 * size_t(n_chunks) * R;
+  const int threads = 128, gx = (R + threads - 1) / threads;
+#define PTB_CHUNK_PASS(P, GY)                                                                                      \
+  rglru_chunk_kernel<T, P><<<dim3(gx, GY), threads, 0, stream>>>(                                                   \
+      gates, (const T*)u, (const T*)y_act, lam, (const T*)proj, bx, state, state_stride, slots, sb, chunk_seq, chunk_q0, \
+      seq_chunk0, n_chunks, chunk_len, agg_a, agg_b, s_start, (T*)out, R, bw, taps, c_decay)
+  PTB_CHUNK_PASS(1, n_chunks);
+  PTB_CHUNK_PASS(2, sb.n_seqs);
+  PTB_CHUNK_PASS(3, n_chunks);
+#undef PTB_CHUNK_PASS
+  return launch_status();
+}
+
 // y[t, g, :] = act(W[g] x[t, g, :] + bias[g]) [* sigmoid(gate[t, g, :])], W [groups, N, K]; x is read with
 // strides (a token's stride xt, a group's stride xg), y [tokens, groups, N] is float32 or the input's
 // type. float32 FMAs in ascending k, 16 products summed apart and then into the total: a row's
@@ -152,7 +230,78 @@ block_linear_kernel(const T* __restrict__ x, long long xt, long long xg, const T
   }
 }
 
+// The same for a few rows (steps of single tokens): a warp per (group, output) reads its row of W once,
+// lanes along K, and forms the sums of all M <= 16 rows; the order of a row's sums is fixed.
+constexpr int SKINNY_M = 16;
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+block_linear_skinny_kernel(const T* __restrict__ x, long long xt, long long xg, const T* __restrict__ w,
+                           const float* __restrict__ bias, TO* __restrict__ y, const T* __restrict__ gate,
+                           long long gate_t, int M, int G, int N, int K, int act) {
+  const int lane = threadIdx.x % 32;
+  const long long item = (long long)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  if (item >= (long long)G * N) return;
+  const int g = int(item / N), n = int(item % N);
+  const T* wr = w + (size_t(g) * N + n) * K;
+  float acc[SKINNY_M];
+#pragma unroll
+  for (int m = 0; m < SKINNY_M; ++m) acc[m] = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float wv = to_f(wr[k]);
+#pragma unroll
+    for (int m = 0; m < SKINNY_M; ++m)
+      if (m < M) acc[m] = fmaf(wv, to_f(x[size_t(m) * xt + size_t(g) * xg + k]), acc[m]);
+  }
+#pragma unroll
+  for (int m = 0; m < SKINNY_M; ++m) {
+    if (m >= M) break;
+    float v = warp_sum(acc[m]);
+    if (lane == 0) {
+      if (bias) v += bias[size_t(g) * N + n];
+      if (act == 1) v = 1.f / (1.f + expf(-v));
+      if (gate) v *= 1.f / (1.f + expf(-to_f(gate[size_t(m) * gate_t + size_t(g) * N + n])));
+      y[(size_t(m) * G + g) * N + n] = from_f<TO>(v);
+    }
+  }
+}
+
+// The epilogue of block_linear for products that the library's batched routine made: z [groups, M, N]
+// (float32 or bfloat16) -> y [M, groups, N] = act(z + bias[g]) [* sigmoid(gate)], float32 sums.
+template <typename TI, typename TO, typename TG>
+__global__ void block_epilogue_kernel(const TI* __restrict__ z, const float* __restrict__ bias, const TG* __restrict__ gate,
+                                      long long gate_t, TO* __restrict__ y, int M, int G, int N, int act) {
+  const size_t total = size_t(M) * G * N, stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int n = int(i % N), g = int((i / N) % G), m = int(i / (size_t(N) * G));
+    float v = to_f(z[(size_t(g) * M + m) * N + n]);
+    if (bias) v += bias[size_t(g) * N + n];
+    if (act == 1) v = 1.f / (1.f + expf(-v));
+    if (gate) v *= 1.f / (1.f + expf(-to_f(gate[size_t(m) * gate_t + size_t(g) * N + n])));
+    y[i] = from_f<TO>(v);
+  }
+}
+
 }  // namespace
+
+PTB_API int ptb_block_epilogue(int in_dtype, int out_dtype, const void* z, const float* bias, const void* gate,
+                               long long gate_t, void* y, int M, int G, int N, int act, cudaStream_t stream) {
+  if (M <= 0 || G <= 0 || N <= 0) return PTB_OK;
+  if (act < 0 || act > 1) return PTB_ERR_SIZE;
+  const size_t total = size_t(M) * G * N, want = (total + 255) / 256, most = size_t(sm_count()) * 16;
+  const int blocks = int(want < most ? want : most);
+  typedef __nv_bfloat16 bf;
+  if (in_dtype == PTB_F32 && out_dtype == PTB_F32)
+    block_epilogue_kernel<float, float, bf><<<blocks, 256, 0, stream>>>((const float*)z, bias, (const bf*)gate, gate_t, (float*)y, M, G, N, act);
+  else if (in_dtype == PTB_F32 && out_dtype == PTB_BF16)
+    block_epilogue_kernel<float, bf, bf><<<blocks, 256, 0, stream>>>((const float*)z, bias, (const bf*)gate, gate_t, (bf*)y, M, G, N, act);
+  else if (in_dtype == PTB_BF16 && out_dtype == PTB_BF16)
+    block_epilogue_kernel<bf, bf, bf><<<blocks, 256, 0, stream>>>((const bf*)z, bias, (const bf*)gate, gate_t, (bf*)y, M, G, N, act);
+  else if (in_dtype == PTB_BF16 && out_dtype == PTB_F32)
+    block_epilogue_kernel<bf, float, bf><<<blocks, 256, 0, stream>>>((const bf*)z, bias, (const bf*)gate, gate_t, (float*)y, M, G, N, act);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}
 
 PTB_API int ptb_rglru_conv(int dtype, const void* proj, const float* by, const float* bx, const float* conv_w,
                            const float* conv_b, const float* state, long long state_stride, const int* slots,
@@ -196,6 +345,27 @@ PTB_API int ptb_rglru_scan(int dtype, const float* gates, const void* u, const v
   return launch_status();
 }
 
+// `work`: 3 * n_chunks * R float32 values
+PTB_API int ptb_rglru_scan_chunks(int dtype, const float* gates, const void* u, const void* y_act, const float* lam,
+                                  const void* proj, const float* bx, float* state, long long state_stride,
+                                  const int* slots, const StepBatch* sb, const int* chunk_seq, const int* chunk_q0,
+                                  const int* seq_chunk0, int n_chunks, int chunk_len, float* work, void* out, int R,
+                                  int blocks_n, int taps, float c_decay, cudaStream_t stream) {
+  if (sb->n_tokens <= 0 || n_chunks <= 0) return PTB_OK;
+  if (R <= 0 || blocks_n <= 0 || R % blocks_n != 0 || taps < 1 || taps > MAX_TAPS || chunk_len <= 0 ||
+      n_chunks > 65535 || sb->n_seqs > 65535)
+    return PTB_ERR_SIZE;
+  if (dtype == PTB_F32)
+    return launch_rglru_chunks<float>(gates, u, y_act, lam, proj, bx, state, state_stride, slots, *sb, chunk_seq,
+                                      chunk_q0, seq_chunk0, n_chunks, chunk_len, work, out, R, R / blocks_n, taps,
+                                      c_decay, stream);
+  if (dtype == PTB_BF16)
+    return launch_rglru_chunks<__nv_bfloat16>(gates, u, y_act, lam, proj, bx, state, state_stride, slots, *sb,
+                                              chunk_seq, chunk_q0, seq_chunk0, n_chunks, chunk_len, work, out, R,
+                                              R / blocks_n, taps, c_decay, stream);
+  return PTB_ERR_DTYPE;
+}
+
 PTB_API int ptb_block_linear(int dtype, int out_dtype, const void* x, long long xt, long long xg, const void* w,
                              const float* bias, void* y, const void* gate, long long gate_t, int M, int G, int N,
                              int K, int act, cudaStream_t stream) {
@@ -203,6 +373,20 @@ PTB_API int ptb_block_linear(int dtype, int out_dtype, const void* x, long long 
   if (K <= 0 || act < 0 || act > 1 || G > 65535) return PTB_ERR_SIZE;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, G);
   if (grid.y > 65535) return PTB_ERR_SIZE;
+  if (M <= SKINNY_M) {
+    const long long items = (long long)G * N;
+    const int sgrid = int((items + 7) / 8);
+    typedef __nv_bfloat16 bf;
+    if (dtype == PTB_F32 && out_dtype == PTB_F32)
+      block_linear_skinny_kernel<float, float><<<sgrid, 256, 0, stream>>>((const float*)x, xt, xg, (const float*)w, bias, (float*)y, (const float*)gate, gate_t, M, G, N, K, act);
+    else if (dtype == PTB_BF16 && out_dtype == PTB_F32)
+      block_linear_skinny_kernel<bf, float><<<sgrid, 256, 0, stream>>>((const bf*)x, xt, xg, (const bf*)w, bias, (float*)y, (const bf*)gate, gate_t, M, G, N, K, act);
+    else if (dtype == PTB_BF16 && out_dtype == PTB_BF16)
+      block_linear_skinny_kernel<bf, bf><<<sgrid, 256, 0, stream>>>((const bf*)x, xt, xg, (const bf*)w, bias, (bf*)y, (const bf*)gate, gate_t, M, G, N, K, act);
+    else
+      return PTB_ERR_DTYPE;
+    return launch_status();
+  }
   if (dtype == PTB_F32 && out_dtype == PTB_F32)
     block_linear_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)x, xt, xg, (const float*)w, bias,
                                                                 (float*)y, (const float*)gate, gate_t, M, G, N, K, act);

@@ -84,7 +84,8 @@ def lib():
                      "ptb_fill_normal", "ptb_selftest_bounded_wait", "ptb_scale", "ptb_selftest_mma_cadence",
                      "ptb_norm_stream", "ptb_add_stream", "ptb_latent_store", "ptb_latent_attention", "ptb_latent_rows",
                      "ptb_rglru_conv", "ptb_rglru_scan", "ptb_block_linear", "ptb_route", "ptb_expert_plan",
-                     "ptb_expert_linear", "ptb_expert_combine"):
+                     "ptb_expert_linear", "ptb_expert_combine", "ptb_expert_linear_mma", "ptb_latent_attention_mma",
+                     "ptb_latent_attention_mma_supports", "ptb_rglru_scan_chunks", "ptb_block_epilogue"):
             getattr(L, name).restype = ctypes.c_int
         L.ptb_latent_part_floats.restype = ctypes.c_longlong
         L.ptb_expert_plan_words.restype = ctypes.c_longlong
@@ -685,13 +686,19 @@ def latent_store(src: torch.Tensor, norm_w: torch.Tensor, eps: float, pool: torc
                                   1 if interleaved else 0, rank, rot_dim, _stream(pool)), "latent_store")
 
 
+def latent_attention_mma_supports(rank: int, rot_dim: int) -> bool:
+    return bool(lib().ptb_latent_attention_mma_supports(int(rank), int(rot_dim)))
+
+
 def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, q_rot_off: int, pool: torch.Tensor, batch: StepBatchC,
                      tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, tile_tokens: int, rope, rank: int,
-                     rot_dim: int, scale: float, interleaved: bool = True, n_splits: int = 1) -> torch.Tensor:
+                     rot_dim: int, scale: float, interleaved: bool = True, n_splits: int = 1,
+                     tensor_cores: Optional[bool] = None) -> torch.Tensor:
     """Causal attention in latent space. ``q_abs`` [tokens, heads, rank] float32 (queries with the key
     up-projection folded in), ``q`` [tokens, heads, q_dim] whose entries from ``q_rot_off`` on are the part
     to rotate, ``pool`` the cache entry's rows [pages, 1, 64, rank + rot_dim]. A tile holds ``tile_tokens``
-    tokens x 16 / tile_tokens heads; ``n_splits`` blocks share a tile's key pages. Returns
+    tokens x 16 / tile_tokens heads; ``n_splits`` blocks share a tile's key pages. bfloat16 with ``rank`` a
+    multiple of 64 and ``rot_dim`` of 16 runs on the tensor cores (``tensor_cores=False``: the general kernel). Returns
     [tokens, heads, rank] in the model dtype: per head, the softmax-weighted sum of the cached latents."""
     _need_cuda(q_abs, q, pool, tile_seq, tile_q0)
     n, heads, q_dim = q.shape
@@ -707,10 +714,19 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, q_rot_off: int, pool:
     if n_splits > 1:
         need = int(lib().ptb_latent_part_floats(n_tiles, heads, heads_per_block, n_splits, rank))
         part = torch.empty(need, dtype=torch.float32, device=q.device)
-    _check(lib().ptb_latent_attention(_dtype_code(q), _ptr(q_abs), _ptr(q), q_dim, q_rot_off, _ptr(pool), _ptr(part),
-                                      _ptr(out), ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(cos),
-                                      _ptr(sin), pairs, 1 if interleaved else 0, heads, rank, rot_dim, tile_tokens,
-                                      heads_per_block, ctypes.c_float(scale), n_splits, _stream(q)), "latent_attention")
+    if tensor_cores is None:
+        tensor_cores = q.dtype == torch.bfloat16 and latent_attention_mma_supports(rank, rot_dim)
+    if tensor_cores:
+        _check(lib().ptb_latent_attention_mma(_ptr(q_abs), _ptr(q), q_dim, q_rot_off, _ptr(pool), _ptr(part), _ptr(out),
+                                              ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(cos),
+                                              _ptr(sin), pairs, 1 if interleaved else 0, heads, rank, rot_dim, tile_tokens,
+                                              heads_per_block, ctypes.c_float(scale), n_splits, _stream(q)),
+               "latent_attention_mma")
+    else:
+        _check(lib().ptb_latent_attention(_dtype_code(q), _ptr(q_abs), _ptr(q), q_dim, q_rot_off, _ptr(pool), _ptr(part),
+                                          _ptr(out), ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(cos),
+                                          _ptr(sin), pairs, 1 if interleaved else 0, heads, rank, rot_dim, tile_tokens,
+                                          heads_per_block, ctypes.c_float(scale), n_splits, _stream(q)), "latent_attention")
     if n_splits > 1:
         global launches
         launches += 1
@@ -719,6 +735,9 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, q_rot_off: int, pool:
 
 # ------------------------------------------------------------------------------------------------
 # Block-diagonal linear layers and the gated linear recurrence
+BLOCK_LINEAR_LIBRARY_ROWS = 256   # rows from which block_linear's product is the library's batched one (bfloat16)
+
+
 def block_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
                  out_dtype: Optional[torch.dtype] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[t, g] = act(w[g] @ x[t, g] + bias[g]) [* sigmoid(gate[t, g])]: ``x`` [tokens, groups, K] (any
@@ -734,6 +753,17 @@ def block_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
         raise KernelError("block_linear: the gate does not fit")
     out_dtype = out_dtype or x.dtype
     y = torch.empty((m, g, n), dtype=out_dtype, device=x.device)
+    if x.dtype == torch.bfloat16 and m >= BLOCK_LINEAR_LIBRARY_ROWS:
+        # many rows in bfloat16: the library's batched product (as the plain linear layers use the library's
+        # product for prompts), float32 out where the result is wanted in float32, then the epilogue
+        if out_dtype == torch.float32:
+            z = torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32)
+        else:
+            z = torch.bmm(x.transpose(0, 1), w.transpose(1, 2))
+        _check(lib().ptb_block_epilogue(_dtype_code(z), _dtype_code(y), _ptr(z), _ptr(bias), _ptr(gate),
+                                        ctypes.c_longlong(0 if gate is None else gate.stride(0)), _ptr(y), m, g, n,
+                                        {"none": 0, "sigmoid": 1}[act], _stream(x)), "block_epilogue")
+        return y
     _check(lib().ptb_block_linear(_dtype_code(x), _dtype_code(y), _ptr(x), ctypes.c_longlong(x.stride(0)),
                                   ctypes.c_longlong(x.stride(1)), _ptr(w), _ptr(bias), _ptr(y), _ptr(gate),
                                   ctypes.c_longlong(0 if gate is None else gate.stride(0)), m, g, n, k,
@@ -777,9 +807,32 @@ def rglru_scan(gates: torch.Tensor, u: torch.Tensor, y_act: torch.Tensor, lam: t
     return out
 
 
+def rglru_scan_chunks(gates: torch.Tensor, u: torch.Tensor, y_act: torch.Tensor, lam: torch.Tensor, proj: torch.Tensor,
+                      bx: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, batch: StepBatchC, blocks: int, taps: int,
+                      decay: float, chunk_seq: torch.Tensor, chunk_q0: torch.Tensor, seq_chunk0: torch.Tensor,
+                      n_chunks: int, chunk_len: int) -> torch.Tensor:
+    """``rglru_scan`` for long prompts: the sequences are cut into chunks of ``chunk_len`` tokens
+    (``chunk_seq``, ``chunk_q0``: sequence and first token of each; ``seq_chunk0``: a sequence's first chunk)
+    that run side by side and are joined in order (three passes)."""
+    _need_cuda(gates, u, y_act, lam, proj, bx, slots, chunk_seq, chunk_q0, seq_chunk0)
+    n, r = u.shape
+    if gates.dtype != torch.float32 or gates.numel() != n * 2 * r or state.stride(1) != 1 or state.shape[1] != r * taps:
+        raise KernelError("rglru_scan_chunks: gates or state do not fit")
+    out = torch.empty_like(u)
+    work = torch.empty(3 * n_chunks * r, dtype=torch.float32, device=u.device)
+    _check(lib().ptb_rglru_scan_chunks(_dtype_code(u), _ptr(gates), _ptr(u), _ptr(y_act), _ptr(lam), _ptr(proj), _ptr(bx),
+                                       _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(slots), ctypes.byref(batch),
+                                       _ptr(chunk_seq), _ptr(chunk_q0), _ptr(seq_chunk0), n_chunks, chunk_len, _ptr(work),
+                                       _ptr(out), r, blocks, taps, ctypes.c_float(decay), _stream(u)), "rglru_scan_chunks")
+    global launches
+    launches += 2
+    return out
+
+
 # ------------------------------------------------------------------------------------------------
 # Routed experts
 EXPERT_TILE_ROWS = (16, 64)   # rows of a tile of the grouped products: few pairs, many pairs
+EXPERT_MMA_TILE_ROWS = 64     # ptb_expert_linear_mma_tile_rows()
 
 
 def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, n_groups: int, keep: int, top: int,
@@ -811,7 +864,9 @@ def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_ga
     n_experts, two_f, _ = w_gate_up.shape
     f = two_f // 2
     pairs = n_tokens * top
-    tile_rows = EXPERT_TILE_ROWS[0] if pairs <= 8 * n_experts else EXPERT_TILE_ROWS[1]
+    # bfloat16 with row sizes in whole 16-byte words: the tensor-core kernel (tiles of 64 rows); else float32 FMAs
+    mma = h.dtype == torch.bfloat16 and width % 8 == 0 and f % 8 == 0
+    tile_rows = EXPERT_MMA_TILE_ROWS if mma else (EXPERT_TILE_ROWS[0] if pairs <= 8 * n_experts else EXPERT_TILE_ROWS[1])
     max_tiles = pairs // tile_rows + min(pairs, n_experts)
     L = lib()
     plan = torch.empty(int(L.ptb_expert_plan_words(pairs, max_tiles)), dtype=torch.int32, device=h.device)
@@ -819,11 +874,17 @@ def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_ga
     _check(L.ptb_expert_plan(_ptr(ids), _ptr(plan), pairs, n_experts, tile_rows, max_tiles, stream), "expert_plan")
     code = _dtype_code(h)
     a = torch.empty((pairs, f), dtype=h.dtype, device=h.device)
-    _check(L.ptb_expert_linear(code, 0, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
-                               tile_rows, stream), "expert_linear (gate, up)")
     y = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
-    _check(L.ptb_expert_linear(code, 1, _ptr(a), _ptr(w_down), _ptr(y), _ptr(plan), pairs, max_tiles, top, width, f,
-                               tile_rows, stream), "expert_linear (down)")
+    if mma:
+        _check(L.ptb_expert_linear_mma(0, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
+                                       stream), "expert_linear_mma (gate, up)")
+        _check(L.ptb_expert_linear_mma(1, _ptr(a), _ptr(w_down), _ptr(y), _ptr(plan), pairs, max_tiles, top, width, f,
+                                       stream), "expert_linear_mma (down)")
+    else:
+        _check(L.ptb_expert_linear(code, 0, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
+                                   tile_rows, stream), "expert_linear (gate, up)")
+        _check(L.ptb_expert_linear(code, 1, _ptr(a), _ptr(w_down), _ptr(y), _ptr(plan), pairs, max_tiles, top, width, f,
+                                   tile_rows, stream), "expert_linear (down)")
     if base is not None and (base.shape != h.shape or base.dtype not in (torch.float32, h.dtype)):
         raise KernelError("routed_experts: base must have the input's shape, in float32 or the input's dtype")
     out = torch.empty((n_tokens, width), dtype=torch.float32 if base is None else base.dtype, device=h.device)

@@ -23,6 +23,28 @@ from .base import BuildContext, ParamDecl, Part, PartSpec, StateNeed, register_p
 from .linear import linear
 
 
+SCAN_CHUNK = 64         # tokens of a chunk of the chunked scan
+SCAN_CHUNKED_FROM = 256  # a step whose longest sequence brings this many tokens scans in chunks
+
+
+class RecurrenceChunks:
+    """The chunked scan's view of a step, as a planner: every sequence's new tokens cut into chunks of
+    ``SCAN_CHUNK`` (sequence and first token of each chunk, and each sequence's first chunk). All recurrent
+    layers of a model share the plan."""
+    plan_key = "recurrence_chunks"
+
+    def plan(self, ctx):
+        from ..engine.batch import StepPlan
+        if max(ctx.new) < SCAN_CHUNKED_FROM:
+            return StepPlan(arrays={}, facts={"n_chunks": 0})
+        seqs, firsts = ctx.tiles(SCAN_CHUNK)
+        first_of, at = [], 0
+        for n in ctx.new:
+            first_of.append(at)
+            at += (n + SCAN_CHUNK - 1) // SCAN_CHUNK
+        return StepPlan(arrays={"chunk_seq": seqs, "chunk_q0": firsts, "seq_chunk0": first_of}, facts={"n_chunks": len(seqs)})
+
+
 @register_part("mixer", "rglru")
 class GatedLinearRecurrence(Part):
     graph_safe = True
@@ -61,6 +83,9 @@ class GatedLinearRecurrence(Part):
     def state_need(self):
         return StateNeed(self.width * self.taps)
 
+    def planner(self):
+        return RecurrenceChunks()
+
     def runs_beside(self, ctx) -> bool:
         return False
 
@@ -72,5 +97,11 @@ class GatedLinearRecurrence(Part):
         slots, batch = ctx.dev["slots"], ctx.batch_c[0]
         y_act, u = k.rglru_conv(proj, self.p_y_b, self.p_x_b, self.p_conv, self.p_conv_b, state, slots, batch)
         gates = k.block_linear(u.view(t, B, R // B), self.p_gates, self.p_gates_b, act="sigmoid", out_dtype=torch.float32)
-        out = k.rglru_scan(gates, u, y_act, self.p_lam, proj, self.p_x_b, state, slots, batch, B, self.taps, self.decay)
+        chunks = ctx.plan(RecurrenceChunks.plan_key)
+        if chunks.facts["n_chunks"]:       # long prompts: chunks side by side, joined in order
+            out = k.rglru_scan_chunks(gates, u, y_act, self.p_lam, proj, self.p_x_b, state, slots, batch, B, self.taps,
+                                      self.decay, chunks.dev["chunk_seq"], chunks.dev["chunk_q0"], chunks.dev["seq_chunk0"],
+                                      chunks.facts["n_chunks"], SCAN_CHUNK)
+        else:
+            out = k.rglru_scan(gates, u, y_act, self.p_lam, proj, self.p_x_b, state, slots, batch, B, self.taps, self.decay)
         return linear(k, out, self.p_o, add=add)

@@ -74,7 +74,7 @@ def test_stream_norm_and_sum(width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m,groups,n,kk", [(1, 3, 20, 24), (70, 5, 14, 10), (130, 1, 80, 80), (9, 18, 64, 32)])
+@pytest.mark.parametrize("m,groups,n,kk", [(1, 3, 20, 24), (70, 5, 14, 10), (130, 1, 80, 80), (9, 18, 64, 32), (300, 4, 40, 24)])
 def test_block_linear(dtype, m, groups, n, kk):
     k = K()
     dt = tdtype(dtype)
@@ -195,7 +195,7 @@ def test_latent_attention_finds_one_far_key(dtype, past, new, pos):
     assert (off - got[last]).abs().max() > 0.1      # another needle gives another row
 
 
-def rglru_case(dtype, R, blocks, taps, pasts, news, seed=0):
+def rglru_case(dtype, R, blocks, taps, pasts, news, seed=0, chunk=0):
     """The recurrence's kernels from random branch projections in two steps; (kernel output, plain) for the
     second step, and the state rows of the slots."""
     from pytorch_transformers_b200.cache.paged import Cache
@@ -229,7 +229,14 @@ def rglru_case(dtype, R, blocks, taps, pasts, news, seed=0):
         p = torch.cat([proj[i][ranges[i][0]:ranges[i][1]] for i in live]).cuda()
         y_act, u = k.rglru_conv(p, by.cuda(), bx.cuda(), conv_w.cuda(), conv_b.cuda(), state, ctx.dev["slots"], ctx.batch_c[0])
         gates = k.block_linear(u.view(-1, blocks, bw), gates_w.cuda(), gates_b.cuda(), act="sigmoid", out_dtype=torch.float32)
-        out = k.rglru_scan(gates, u, y_act, lam.cuda(), p, bx.cuda(), state, ctx.dev["slots"], ctx.batch_c[0], blocks, taps, 8.0)
+        if chunk:       # the chunked scan: chunks side by side, joined in order
+            seqs, firsts = ctx.tiles(chunk)
+            first_of = [sum((n + chunk - 1) // chunk for n in ctx.new[:b]) for b in range(ctx.n_seqs)]
+            ints = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+            out = k.rglru_scan_chunks(gates, u, y_act, lam.cuda(), p, bx.cuda(), state, ctx.dev["slots"], ctx.batch_c[0], blocks,
+                                      taps, 8.0, ints(seqs), ints(firsts), ints(first_of), len(seqs), chunk)
+        else:
+            out = k.rglru_scan(gates, u, y_act, lam.cuda(), p, bx.cuda(), state, ctx.dev["slots"], ctx.batch_c[0], blocks, taps, 8.0)
         ctx.commit()
         return out, live
 
@@ -262,6 +269,16 @@ def rglru_case(dtype, R, blocks, taps, pasts, news, seed=0):
 def test_recurrence_in_two_steps_equals_whole(dtype, R, blocks, taps):
     for pasts, news in [((0, 0), (1, 40)), ((1, 2, 3, 7), (1, 1, 1, 1)), ((5, 1), (2, 30)), ((90,), (1,))]:
         got, ref = rglru_case(dtype, R, blocks, taps, pasts, news, seed=R + taps)
+        torch.testing.assert_close(got, ref, **({"atol": 2e-5, "rtol": 1e-4} if dtype == "float32" else {"atol": 3e-2, "rtol": 3e-2}))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("chunk", [1, 7, 64])
+def test_recurrence_scanned_in_chunks(dtype, chunk):
+    """Chunks of 1, of 7 (a ragged last chunk) and of 64 tokens, from an empty state and from a carried one,
+    and the state they leave: a third step of single tokens goes on from it."""
+    for pasts, news in [((0, 0, 0), (130, 1, 64)), ((5, 70), (129, 3))]:
+        got, ref = rglru_case(dtype, 96, 3, 4, pasts, news, seed=chunk, chunk=chunk)
         torch.testing.assert_close(got, ref, **({"atol": 2e-5, "rtol": 1e-4} if dtype == "float32" else {"atol": 3e-2, "rtol": 3e-2}))
 
 
@@ -366,8 +383,8 @@ NAMES = sorted(pm.CONFIGS)
 def test_each_request_alone_and_whole(loaded, name, dtype):
     L = loaded(name, dtype)
     assert L.model.spec.stream_float32 and L.model.use_graphs
-    cache = L.model.new_cache(256)
-    for ids in pm.prompts(L.cfg, (1, 2, 5, 70, 129), seed=1):
+    cache = L.model.new_cache(320)
+    for ids in pm.prompts(L.cfg, (1, 2, 5, 70, 129, 300), seed=1):
         s = cache.open()
         close(L.model.step(cache, [s], [ids], want="all"), L.plain_logits(ids), dtype, f"{name} {len(ids)} tokens")
         cache.close(s)
