@@ -361,7 +361,8 @@ PTB_API int ptb_latent_attention(int dtype, const float* q_abs, const void* q, i
 // of 64 and rot_dim a multiple of 16. A block of 4 warps takes the 16 rows of a tile (the heads of a
 // token in a step of single tokens) and walks its share of the key pages. A page [64][rank + rot_dim]
 // comes into shared memory once (cp.async, rows 16 bytes apart from a multiple of 128 so that ldmatrix
-// meets no bank twice) and serves both products: warp w forms the scores of keys 16 w .. 16 w + 15
+// meets no bank twice) and serves both products, for up to four groups of 4 warps with 16 rows each (a tile of a
+// prompt is 16 tokens x 4 heads, so that a staged page meets 64 rows): warp w of a group forms the scores of keys 16 w .. 16 w + 15
 // (S = Q K^T over all rank + rot_dim entries), the warps exchange row maxima and sums through shared
 // memory, the weights go to shared memory as bfloat16, and warp w adds P V for the columns
 // w rank / 4 .. (w + 1) rank / 4 of the output, V being the first `rank` entries of the same rows.
@@ -373,8 +374,10 @@ namespace {
 
 constexpr int MTHREADS = 128;
 
-template <int NF>   // 8-column fragments of the output per warp: rank = 32 NF
-__global__ void __launch_bounds__(MTHREADS)
+// NF: 8-column fragments of the output per warp (rank = 32 NF). TG: groups of 4 warps; every group has 16
+// rows of the tile (a tile of a prompt holds 16 TG rows: tokens x heads), and all groups use one staged page.
+template <int NF, int TG>
+__global__ void __launch_bounds__(MTHREADS * TG)
 latent_attention_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __restrict__ q, int q_dim,
                             int q_rot_off, const __nv_bfloat16* __restrict__ pool, float* __restrict__ part,
                             __nv_bfloat16* __restrict__ out, StepBatch sb, const int* __restrict__ tile_seq,
@@ -382,23 +385,28 @@ latent_attention_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16
                             const float* __restrict__ rope_sin, int rot_pairs, int interleaved, int heads, int rank,
                             int rot_dim, int tile_tokens, int heads_per_block, float scale, int n_splits) {
   extern __shared__ __align__(128) unsigned char msm[];
+  constexpr int NT = MTHREADS * TG, QROWS = ROWS * TG;
   const int dk = rank + rot_dim;
   const int rowb = dk * 2 + 16;                       // bytes of a staged row
-  unsigned char* q_s = msm;                           // [16][rowb]
-  unsigned char* k_s = q_s + 16 * rowb;               // [64][rowb]
-  unsigned char* p_s = k_s + PTB_PAGE * rowb;         // [16][144]: 64 weights and 16 bytes of padding
-  float* wmax = reinterpret_cast<float*>(p_s + 16 * 144);   // [4][16]
-  float* wsum = wmax + 64;                                  // [4][16]
+  unsigned char* q_s = msm;                           // [16 TG][rowb]
+  unsigned char* k_s = q_s + QROWS * rowb;            // [64][rowb]
+  unsigned char* p_all = k_s + PTB_PAGE * rowb;       // [TG][16][144]: 64 weights and 16 bytes of padding a row
+  float* wmax_all = reinterpret_cast<float*>(p_all + TG * 16 * 144);   // [TG][4][16]
+  float* wsum_all = wmax_all + TG * 64;                                 // [TG][4][16]
 
   const int tile = blockIdx.x, h0 = blockIdx.y * heads_per_block, split = blockIdx.z;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
   const int n_new = sb.seq_new[seq], past = sb.seq_past[seq], start = sb.seq_start[seq];
   const int toks = min(tile_tokens, n_new - q0);
-  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int tid = threadIdx.x, lane = tid % 32;
+  const int tg = tid / MTHREADS, warp = (tid / 32) % 4;      // group of warps, warp in the group
   const int used_rows = tile_tokens * heads_per_block;
+  unsigned char* p_s = p_all + tg * 16 * 144;
+  float* wmax = wmax_all + tg * 64;
+  float* wsum = wsum_all + tg * 64;
 
   // the query rows, rounded to bfloat16: [q_abs | rotated part]
-  for (int i = tid; i < ROWS * rank; i += MTHREADS) {
+  for (int i = tid; i < QROWS * rank; i += NT) {
     const int rr = i / rank, e = i % rank;
     const int ti = rr / heads_per_block, hh = h0 + rr % heads_per_block;
     const bool ok = ti < toks && hh < heads && rr < used_rows;
@@ -406,7 +414,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16
     reinterpret_cast<__nv_bfloat16*>(q_s + rr * rowb)[e] = __float2bfloat16_rn(v);
   }
   const int items = rot_pairs + (rot_dim - 2 * rot_pairs);
-  for (int i = tid; i < ROWS * items; i += MTHREADS) {
+  for (int i = tid; i < QROWS * items; i += NT) {
     const int rr = i / items, e = i % items;
     const int ti = rr / heads_per_block, hh = h0 + rr % heads_per_block;
     const bool ok = ti < toks && hh < heads && rr < used_rows;
@@ -425,12 +433,12 @@ latent_attention_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16
     }
   }
 
-  // this thread's two rows of the 16 (accumulator layout of mma.m16n8k16)
+  // this thread's two rows of its group's 16 (accumulator layout of mma.m16n8k16)
   const int r_lo = lane / 4, r_hi = r_lo + 8;
   int pos_of[2];
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
-    const int rr = hf ? r_hi : r_lo;
+    const int rr = tg * 16 + (hf ? r_hi : r_lo);
     const int ti = rr / heads_per_block, hh = h0 + rr % heads_per_block;
     pos_of[hf] = (ti < toks && hh < heads && rr < used_rows) ? past + q0 + ti : -1;
   }
@@ -447,13 +455,13 @@ latent_attention_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16
   const int kb_lo = split * per, kb_hi = min(n_blocks, kb_lo + per) - 1;
   const int* pages = sb.pages + size_t(seq) * sb.pages_stride;
   const int chunks = dk / 8;
-  const uint32_t q_base = smem_u32(q_s), k_base = smem_u32(k_s), p_base = smem_u32(p_s);
+  const uint32_t q_base = smem_u32(q_s) + tg * 16 * rowb, k_base = smem_u32(k_s), p_base = smem_u32(p_s);
   const int col0 = warp * NF * 8;       // first output column of this warp
 
   for (int kb = kb_lo; kb <= kb_hi; ++kb) {
     const __nv_bfloat16* kp = pool + kv_offset(pages[kb], 0, 0, 1, dk);
     __syncthreads();   // the page before is no longer read (and the query rows are written)
-    for (int i = tid; i < PTB_PAGE * chunks; i += MTHREADS) {
+    for (int i = tid; i < PTB_PAGE * chunks; i += NT) {
       const int j = i / chunks, c = i % chunks;
       cp_async16(k_base + j * rowb + c * 16, kp + size_t(j) * dk + c * 8);
     }
@@ -500,8 +508,8 @@ latent_attention_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16
       const int rr = hf ? r_hi : r_lo;
       const float mb = fmaxf(fmaxf(wmax[rr], wmax[16 + rr]), fmaxf(wmax[32 + rr], wmax[48 + rr]));
       m_new[hf] = fmaxf(m_run[hf], mb);
-      corr[hf] = (m_run[hf] == -INFINITY) ? 0.f : expf(m_run[hf] - m_new[hf]);     // m_new = -inf: nothing seen, sums stay 0
-      if (m_new[hf] == -INFINITY) corr[hf] = 1.f;
+      corr[hf] = (m_run[hf] == -INFINITY) ? 0.f : expf(m_run[hf] - m_new[hf]);
+      if (m_new[hf] == -INFINITY) corr[hf] = 1.f;      // nothing seen yet: the sums stay 0
     }
 #pragma unroll
     for (int f = 0; f < 2; ++f)
@@ -557,10 +565,10 @@ latent_attention_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16
   const int c0 = (lane % 4) * 2;
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
-    const int rr = hf ? r_hi : r_lo;
-    if (n_splits > 1) {
+    const int rl = hf ? r_hi : r_lo, rr = tg * 16 + rl;
+    if (n_splits > 1) {      // only with TG = 1
       float* p = part + ((size_t(tile) * gridDim.y + blockIdx.y) * n_splits + split) * ROWS * size_t(rank + 2) +
-                 size_t(rr) * (rank + 2);
+                 size_t(rl) * (rank + 2);
       if (warp == 0 && lane % 4 == 0) {
         p[0] = m_run[hf];
         p[1] = l_run[hf];
@@ -581,23 +589,23 @@ latent_attention_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16
   }
 }
 
-template <int NF>
-int launch_latent_mma(const float* q_abs, const void* q, int q_dim, int q_rot_off, const void* pool, float* part,
-                      void* out, const StepBatch& sb, const int* tile_seq, const int* tile_q0, int n_tiles,
-                      const float* rope_cos, const float* rope_sin, int rot_pairs, int interleaved, int heads, int rank,
-                      int rot_dim, int tile_tokens, int heads_per_block, float scale, int n_splits, cudaStream_t stream) {
+template <int NF, int TG>
+int launch_latent_mma_tg(const float* q_abs, const void* q, int q_dim, int q_rot_off, const void* pool, float* part,
+                         void* out, const StepBatch& sb, const int* tile_seq, const int* tile_q0, int n_tiles,
+                         const float* rope_cos, const float* rope_sin, int rot_pairs, int interleaved, int heads, int rank,
+                         int rot_dim, int tile_tokens, int heads_per_block, float scale, int n_splits, cudaStream_t stream) {
   const int rowb = (rank + rot_dim) * 2 + 16;
-  const size_t smem = size_t(16 + PTB_PAGE) * rowb + 16 * 144 + 2 * 64 * sizeof(float);
+  const size_t smem = size_t(16 * TG + PTB_PAGE) * rowb + TG * (16 * 144 + 2 * 64 * sizeof(float));
   if (smem > 220 * 1024) return PTB_ERR_SIZE;
   static size_t configured = 48 * 1024;
   if (smem > configured) {
-    if (cudaFuncSetAttribute(latent_attention_mma_kernel<NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+    if (cudaFuncSetAttribute(latent_attention_mma_kernel<NF, TG>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
         cudaSuccess)
       return PTB_ERR_LAUNCH;
     configured = smem;
   }
   const int chunks = (heads + heads_per_block - 1) / heads_per_block;
-  latent_attention_mma_kernel<NF><<<dim3(n_tiles, chunks, n_splits), MTHREADS, smem, stream>>>(
+  latent_attention_mma_kernel<NF, TG><<<dim3(n_tiles, chunks, n_splits), MTHREADS * TG, smem, stream>>>(
       q_abs, (const __nv_bfloat16*)q, q_dim, q_rot_off, (const __nv_bfloat16*)pool, part, (__nv_bfloat16*)out, sb,
       tile_seq, tile_q0, rope_cos, rope_sin, rot_pairs, interleaved, heads, rank, rot_dim, tile_tokens, heads_per_block,
       scale, n_splits);
@@ -606,6 +614,23 @@ int launch_latent_mma(const float* q_abs, const void* q, int q_dim, int q_rot_of
   latent_join_kernel<__nv_bfloat16><<<dim3(n_tiles, chunks, ROWS), 128, n_splits * sizeof(float), stream>>>(
       part, (__nv_bfloat16*)out, sb, tile_seq, tile_q0, heads, rank, tile_tokens, heads_per_block, n_splits);
   return launch_status();
+}
+
+template <int NF>
+int launch_latent_mma(const float* q_abs, const void* q, int q_dim, int q_rot_off, const void* pool, float* part,
+                      void* out, const StepBatch& sb, const int* tile_seq, const int* tile_q0, int n_tiles,
+                      const float* rope_cos, const float* rope_sin, int rot_pairs, int interleaved, int heads, int rank,
+                      int rot_dim, int tile_tokens, int heads_per_block, float scale, int n_splits, cudaStream_t stream) {
+  const int rows = tile_tokens * heads_per_block;
+#define PTB_LTG(TGV)                                                                                                  \
+  return launch_latent_mma_tg<NF, TGV>(q_abs, q, q_dim, q_rot_off, pool, part, out, sb, tile_seq, tile_q0, n_tiles,     \
+                                       rope_cos, rope_sin, rot_pairs, interleaved, heads, rank, rot_dim, tile_tokens,   \
+                                       heads_per_block, scale, n_splits, stream)
+  if (rows <= 16) PTB_LTG(1);
+  if (n_splits != 1) return PTB_ERR_SIZE;
+  if (rows <= 32) PTB_LTG(2);
+  PTB_LTG(4);
+#undef PTB_LTG
 }
 
 }  // namespace
@@ -621,7 +646,7 @@ PTB_API int ptb_latent_attention_mma(const float* q_abs, const void* q, int q_di
                                      int heads_per_block, float scale, int n_splits, cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
   if (!ptb_latent_attention_mma_supports(rank, rot_dim) || heads <= 0 || rot_pairs < 0 || 2 * rot_pairs > rot_dim ||
-      tile_tokens <= 0 || heads_per_block <= 0 || tile_tokens * heads_per_block > ROWS || n_splits < 1 ||
+      tile_tokens <= 0 || heads_per_block <= 0 || tile_tokens * heads_per_block > 4 * ROWS || n_splits < 1 ||
       n_splits > 65535 || (heads + heads_per_block - 1) / heads_per_block > 65535)
     return PTB_ERR_SIZE;
   if (n_splits > 1 && part == nullptr) return PTB_ERR_SIZE;

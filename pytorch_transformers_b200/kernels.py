@@ -706,7 +706,12 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, q_rot_off: int, pool:
         raise KernelError("latent_attention: q_abs must be float32 [tokens, heads, rank] and the pool of q's dtype")
     if pool.shape[-1] != rank + rot_dim or q_rot_off + rot_dim > q_dim:
         raise KernelError("latent_attention: sizes do not fit")
+    if tensor_cores is None:
+        tensor_cores = q.dtype == torch.bfloat16 and latent_attention_mma_supports(rank, rot_dim)
     heads_per_block = max(1, LATENT_ROWS // tile_tokens)
+    if tensor_cores and n_splits == 1 and tile_tokens * heads_per_block == LATENT_ROWS:
+        # the tensor-core kernel takes up to four groups of 16 rows on one staged page: more heads a block
+        heads_per_block *= 4 if heads >= 4 * heads_per_block else (2 if heads >= 2 * heads_per_block else 1)
     out = torch.empty((n, heads, rank), dtype=q.dtype, device=q.device)
     cos, sin = rope if rope is not None else (None, None)
     pairs = 0 if cos is None else cos.shape[1]
@@ -714,8 +719,6 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, q_rot_off: int, pool:
     if n_splits > 1:
         need = int(lib().ptb_latent_part_floats(n_tiles, heads, heads_per_block, n_splits, rank))
         part = torch.empty(need, dtype=torch.float32, device=q.device)
-    if tensor_cores is None:
-        tensor_cores = q.dtype == torch.bfloat16 and latent_attention_mma_supports(rank, rot_dim)
     if tensor_cores:
         _check(lib().ptb_latent_attention_mma(_ptr(q_abs), _ptr(q), q_dim, q_rot_off, _ptr(pool), _ptr(part), _ptr(out),
                                               ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(cos),
