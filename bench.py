@@ -673,10 +673,14 @@ def run_pafevik(args):
                         "decode_ms_per_step": round(dec_ms, 4), "decode_tokens_per_s": round(batch / dec_ms * 1e3, 1),
                         "weight_GB": round(weights / 1e9, 3),
                         "decode_weight_GBps": round(weights / dec_ms / 1e6, 1),
-                        "prefill_kernels_ms": pre_kernels, "decode_kernels_ms": dec_kernels}
+                        "prefill_kernels_ms": pre_kernels,
+                        # launched one by one the decode step is paced by the host: these are upper bounds
+                        "decode_kernels_ms": dec_kernels}
         del cache
         torch.cuda.empty_cache()
-    # the new kernels against their rooflines (algorithmic bytes or FLOPs over the measured peaks)
+    # the prompt's kernels against their rooflines (algorithmic FLOPs or bytes; a prompt's launches are paced by the
+    # device, so the event pairs around them hold). The kernels of a step of single tokens are listed with their
+    # device times under profiles/ (launch lists): launched one by one such a step is paced by the host.
     m = raw["layers"][0]["mixer"]
     H, dk, rank = m["heads"], m["kv_rank"] + m["rot_dim"], m["kv_rank"]
     pairs = tokens * 6
@@ -688,28 +692,28 @@ def run_pafevik(args):
     roof = {}
     t = per_call(P["prefill_kernels_ms"], "latent_attention")
     if t:
-        roof["latent_attention_prefill_TFLOPs_as_run"] = round(P.get("latent_prefill_flops", H * tokens * (tokens + 1) / 2 * 2 * (dk + rank)) / t / 1e9, 1)
+        roof["latent_attention_prefill_TFLOPs_as_run"] = round(H * tokens * (tokens + 1) / 2 * 2 * (dk + rank) / t / 1e9, 1)
+        roof["latent_attention_prefill_frac_of_burst"] = round(roof["latent_attention_prefill_TFLOPs_as_run"] / pk["bf16_tflops"], 3)
     t = per_call(F["prefill_kernels_ms"], "attention_tc")
     if t:
         roof["falcon_attention_prefill_TFLOPs"] = round(H * tokens * (tokens + 1) / 2 * 4 * 128 / t / 1e9, 1)
-    t = per_call(P["decode_kernels_ms"], "latent_attention")
-    if t:
-        roof["latent_attention_decode_GBps"] = round(batch * context * dk * 2 / t / 1e6, 1)
-    for key in ("attention_decode", "attention_decode_tc"):
-        t = per_call(F["decode_kernels_ms"], key)
-        if t:
-            roof["falcon_" + key + "_GBps"] = round(batch * context * 2 * H * 128 * 2 / t / 1e6, 1)
+        roof["falcon_attention_prefill_frac_of_burst"] = round(roof["falcon_attention_prefill_TFLOPs"] / pk["bf16_tflops"], 3)
     t = per_call(P["prefill_kernels_ms"], "routed_experts")
     if t:
         roof["experts_prefill_TFLOPs"] = round(pairs * 3 * 2 * raw["width"] * 1408 / t / 1e9, 1)
-    t = per_call(P["decode_kernels_ms"], "routed_experts")
-    if t:
-        touched = min(64, batch * 6)
-        roof["experts_decode_GBps_at_most"] = round(touched * 3 * raw["width"] * 1408 * 2 / t / 1e6, 1)
+        roof["experts_prefill_frac_of_burst"] = round(roof["experts_prefill_TFLOPs"] / pk["bf16_tflops"], 3)
+    ff = falcon_beside(args.size)["ffn_hidden_size"]
+    t = F["prefill_kernels_ms"].get("matmul_nt")
+    if t:   # all of Falcon's products of the prompt, the library's
+        h = raw["width"]
+        flops = 4 * 2 * tokens * (3 * h * h + h * h + 2 * ff * h)
+        roof["falcon_library_products_TFLOPs"] = round(flops / t["ms"] / 1e9, 1)
+        roof["falcon_library_products_frac_of_burst"] = round(roof["falcon_library_products_TFLOPs"] / pk["bf16_tflops"], 3)
     t = per_call(P["prefill_kernels_ms"], "rglru_scan_chunks")
     if t:
         R = raw["layers"][1]["mixer"]["width"]
-        roof["rglru_scan_prefill_GBps"] = round(tokens * R * (8 + 2 + 2 + 2) / t / 1e6, 1)
+        roof["rglru_scan_prefill_GBps"] = round(tokens * R * (8 + 2 + 2 + 2) / t / 1e6, 1)     # gates, u, y in; out
+        roof["rglru_scan_prefill_frac_of_hbm"] = round(roof["rglru_scan_prefill_GBps"] / pk["hbm_gbs"], 3)
     result["roofline"] = roof
     result["peaks"] = pk
     print(json.dumps(result))

@@ -11,31 +11,52 @@
 namespace {
 
 constexpr int ROUTE_VPL = 16;   // router outputs per lane: up to 512 outputs
-constexpr int ROUTE_WARPS = 16;
+constexpr int ROUTE_WARPS = 8;
 
-// One block per token. The warps share the outputs' dot products (a warp per output, lanes along the
-// width, a fixed order of sums whatever else is in the batch); warp 0 then scores and chooses.
-template <typename T>
+constexpr int ROUTE_TOKENS = 8;   // tokens of a block of the logits kernel for prompts: a matrix row is read once for them
+
+// Router logits z[t, e] = W_r[e] . h[t] in float32: a warp per output, lanes along the width, TPB tokens a
+// block; a token's sums have one fixed order whatever else is in the batch.
+template <typename T, int TPB>
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
-route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ correction,
-             int* __restrict__ ids, float* __restrict__ gates, int n_tokens, int width, int n, int n_groups, int keep,
-             int top, float route_scale) {
-  extern __shared__ float sm[];   // n logits, n choice scores, n_groups group scores
+route_logits_kernel(const T* __restrict__ h, const float* __restrict__ w_router, float* __restrict__ z, int n_tokens,
+                    int width, int n) {
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int t = blockIdx.x;
-  float* zs = sm;
-  float* choice = zs + n;
-  float* gscore = choice + n;
-  const T* x = h + size_t(t) * width;
-  for (int e = warp; e < n; e += ROUTE_WARPS) {
-    const float* wr = w_router + size_t(e) * width;
-    float d = 0.f;
-    for (int k = lane; k < width; k += 32) d = fmaf(wr[k], to_f(x[k]), d);
-    d = warp_sum(d);
-    if (lane == 0) zs[e] = d;
+  const int t0 = blockIdx.x * TPB, e = blockIdx.y * ROUTE_WARPS + warp;
+  if (e >= n) return;
+  const float* wr = w_router + size_t(e) * width;
+  float d[TPB];
+  const T* rows[TPB];      // a token past the end reads the block's first token; its result is not written
+#pragma unroll
+  for (int i = 0; i < TPB; ++i) {
+    d[i] = 0.f;
+    rows[i] = h + size_t(t0 + i < n_tokens ? t0 + i : t0) * width;
   }
-  __syncthreads();
-  if (warp != 0) return;
+#pragma unroll 4
+  for (int k = lane; k < width; k += 32) {
+    const float wv = wr[k];
+#pragma unroll
+    for (int i = 0; i < TPB; ++i) d[i] = fmaf(wv, to_f(rows[i][k]), d[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < TPB; ++i) {
+    const float v = warp_sum(d[i]);
+    if (lane == 0 && t0 + i < n_tokens) z[size_t(t0 + i) * n + e] = v;
+  }
+}
+
+// Scores and choice from the logits: a warp per token.
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+route_select_kernel(const float* __restrict__ zs_all, const float* __restrict__ correction, int* __restrict__ ids,
+                    float* __restrict__ gates, int n_tokens, int n, int n_groups, int keep, int top,
+                    float route_scale) {
+  extern __shared__ float sm[];   // per warp: n choice scores, n_groups group scores
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= n_tokens) return;
+  const float* zs = zs_all + size_t(t) * n;
+  float* choice = sm + size_t(warp) * (n + n_groups);
+  float* gscore = choice + n;
   float z[ROUTE_VPL], s[ROUTE_VPL];
   float zmax = -INFINITY;
 #pragma unroll
@@ -270,7 +291,7 @@ __global__ void expert_combine_kernel(const TB* __restrict__ base, const T* __re
                                       const float* __restrict__ gates, const int* __restrict__ row_of_pair,
                                       TB* __restrict__ out, int width, int top) {
   const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += gridDim.y * blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < top; ++k) {
       const int row = row_of_pair[size_t(t) * top + k];
@@ -298,23 +319,33 @@ int launch_expert_linear(const void* x, const void* w, void* out, const int* pla
 
 }  // namespace
 
-PTB_API int ptb_route(int dtype, const void* h, const float* w_router, const float* correction, int* ids, float* gates,
-                      int n_tokens, int width, int n, int n_groups, int keep, int top, float route_scale,
+// `logits`: float32 scratch [n_tokens, n]
+PTB_API int ptb_route(int dtype, const void* h, const float* w_router, const float* correction, float* logits, int* ids,
+                      float* gates, int n_tokens, int width, int n, int n_groups, int keep, int top, float route_scale,
                       cudaStream_t stream) {
   if (n_tokens <= 0) return PTB_OK;
   if (n <= 0 || n > 32 * ROUTE_VPL || n_groups <= 0 || n % n_groups != 0 || keep <= 0 || keep > n_groups || top <= 0 ||
       top > (n / n_groups) * keep || width <= 0)
     return PTB_ERR_SIZE;
-  const size_t smem = size_t(2 * n + n_groups) * sizeof(float);
-  const int grid = n_tokens;
-  if (dtype == PTB_F32)
-    route_kernel<float><<<grid, 32 * ROUTE_WARPS, smem, stream>>>((const float*)h, w_router, correction, ids, gates,
-                                                                  n_tokens, width, n, n_groups, keep, top, route_scale);
-  else if (dtype == PTB_BF16)
-    route_kernel<__nv_bfloat16><<<grid, 32 * ROUTE_WARPS, smem, stream>>>(
-        (const __nv_bfloat16*)h, w_router, correction, ids, gates, n_tokens, width, n, n_groups, keep, top, route_scale);
-  else
+  // few tokens (steps of single tokens): one token a block, so that the blocks fill the device
+  const int tpb = n_tokens >= 2 * sm_count() ? ROUTE_TOKENS : 1;
+  dim3 grid((n_tokens + tpb - 1) / tpb, (n + ROUTE_WARPS - 1) / ROUTE_WARPS);
+#define PTB_ROUTE(TT, NTOK) \
+  route_logits_kernel<TT, NTOK><<<grid, 32 * ROUTE_WARPS, 0, stream>>>((const TT*)h, w_router, logits, n_tokens, width, n)
+  if (dtype == PTB_F32) {
+    if (tpb == 1) PTB_ROUTE(float, 1);
+    else PTB_ROUTE(float, ROUTE_TOKENS);
+  } else if (dtype == PTB_BF16) {
+    if (tpb == 1) PTB_ROUTE(__nv_bfloat16, 1);
+    else PTB_ROUTE(__nv_bfloat16, ROUTE_TOKENS);
+  } else {
     return PTB_ERR_DTYPE;
+  }
+#undef PTB_ROUTE
+  if (launch_status() != PTB_OK) return PTB_ERR_LAUNCH;
+  const size_t smem = size_t(ROUTE_WARPS) * (n + n_groups) * sizeof(float);
+  route_select_kernel<<<(n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, 32 * ROUTE_WARPS, smem, stream>>>(
+      logits, correction, ids, gates, n_tokens, n, n_groups, keep, top, route_scale);
   return launch_status();
 }
 
@@ -353,14 +384,17 @@ PTB_API int ptb_expert_combine(int dtype, int out_dtype, const void* base, const
   if (n_tokens <= 0) return PTB_OK;
   if (width <= 0 || top <= 0) return PTB_ERR_SIZE;
   const int threads = width >= 1024 ? 256 : 128;
+  // few tokens: several blocks a token, so that the blocks fill the device
+  const int per_token = n_tokens >= 2 * sm_count() ? 1 : (width + threads - 1) / threads;
+  const dim3 n_tokens_grid(n_tokens, per_token);
   if (dtype == PTB_F32 && out_dtype == PTB_F32)
-    expert_combine_kernel<float, float><<<n_tokens, threads, 0, stream>>>(
+    expert_combine_kernel<float, float><<<n_tokens_grid, threads, 0, stream>>>(
         (const float*)base, (const float*)h, y, ids, gates, row_of_pair, (float*)out, width, top);
   else if (dtype == PTB_BF16 && out_dtype == PTB_F32)
-    expert_combine_kernel<__nv_bfloat16, float><<<n_tokens, threads, 0, stream>>>(
+    expert_combine_kernel<__nv_bfloat16, float><<<n_tokens_grid, threads, 0, stream>>>(
         (const float*)base, (const __nv_bfloat16*)h, y, ids, gates, row_of_pair, (float*)out, width, top);
   else if (dtype == PTB_BF16 && out_dtype == PTB_BF16)
-    expert_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+    expert_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<n_tokens_grid, threads, 0, stream>>>(
         (const __nv_bfloat16*)base, (const __nv_bfloat16*)h, y, ids, gates, row_of_pair, (__nv_bfloat16*)out, width,
         top);
   else

@@ -233,11 +233,27 @@ block_linear_kernel(const T* __restrict__ x, long long xt, long long xg, const T
 // The same for a few rows (steps of single tokens): a warp per (group, output) reads its row of W once,
 // lanes along K, and forms the sums of all M <= 16 rows; the order of a row's sums is fixed.
 constexpr int SKINNY_M = 16;
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&f)[8], bool vec);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&f)[8], bool) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = p[i];
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8], bool vec) {
+  if (vec) {
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(p), f);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(p[i]);
+  }
+}
+
+// `vec`: every row of x and w starts on a 16-byte boundary and K is a multiple of 8 (the host checks):
+// bfloat16 operands then move in 16-byte words. A lane takes 8 consecutive k at a time.
 template <typename T, typename TO>
 __global__ void __launch_bounds__(256)
 block_linear_skinny_kernel(const T* __restrict__ x, long long xt, long long xg, const T* __restrict__ w,
                            const float* __restrict__ bias, TO* __restrict__ y, const T* __restrict__ gate,
-                           long long gate_t, int M, int G, int N, int K, int act) {
+                           long long gate_t, int M, int G, int N, int K, int act, int vec) {
   const int lane = threadIdx.x % 32;
   const long long item = (long long)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
   if (item >= (long long)G * N) return;
@@ -246,7 +262,23 @@ block_linear_skinny_kernel(const T* __restrict__ x, long long xt, long long xg, 
   float acc[SKINNY_M];
 #pragma unroll
   for (int m = 0; m < SKINNY_M; ++m) acc[m] = 0.f;
-  for (int k = lane; k < K; k += 32) {
+  const int k_whole = K / 8 * 8;
+  for (int k = lane * 8; k < k_whole; k += 256) {
+    float wv[8];
+    load8<T>(wr + k, wv, vec);
+#pragma unroll
+    for (int m = 0; m < SKINNY_M; ++m) {
+      if (m < M) {
+        float xv[8];
+        load8<T>(x + size_t(m) * xt + size_t(g) * xg + k, xv, vec);
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) part = fmaf(wv[i], xv[i], part);
+        acc[m] += part;
+      }
+    }
+  }
+  for (int k = k_whole + lane; k < K; k += 32) {
     const float wv = to_f(wr[k]);
 #pragma unroll
     for (int m = 0; m < SKINNY_M; ++m)
@@ -377,12 +409,13 @@ PTB_API int ptb_block_linear(int dtype, int out_dtype, const void* x, long long 
     const long long items = (long long)G * N;
     const int sgrid = int((items + 7) / 8);
     typedef __nv_bfloat16 bf;
+    const int vec = (K % 8 == 0 && xt % 8 == 0 && xg % 8 == 0 && aligned16(x) && aligned16(w)) ? 1 : 0;
     if (dtype == PTB_F32 && out_dtype == PTB_F32)
-      block_linear_skinny_kernel<float, float><<<sgrid, 256, 0, stream>>>((const float*)x, xt, xg, (const float*)w, bias, (float*)y, (const float*)gate, gate_t, M, G, N, K, act);
+      block_linear_skinny_kernel<float, float><<<sgrid, 256, 0, stream>>>((const float*)x, xt, xg, (const float*)w, bias, (float*)y, (const float*)gate, gate_t, M, G, N, K, act, vec);
     else if (dtype == PTB_BF16 && out_dtype == PTB_F32)
-      block_linear_skinny_kernel<bf, float><<<sgrid, 256, 0, stream>>>((const bf*)x, xt, xg, (const bf*)w, bias, (float*)y, (const bf*)gate, gate_t, M, G, N, K, act);
+      block_linear_skinny_kernel<bf, float><<<sgrid, 256, 0, stream>>>((const bf*)x, xt, xg, (const bf*)w, bias, (float*)y, (const bf*)gate, gate_t, M, G, N, K, act, vec);
     else if (dtype == PTB_BF16 && out_dtype == PTB_BF16)
-      block_linear_skinny_kernel<bf, bf><<<sgrid, 256, 0, stream>>>((const bf*)x, xt, xg, (const bf*)w, bias, (bf*)y, (const bf*)gate, gate_t, M, G, N, K, act);
+      block_linear_skinny_kernel<bf, bf><<<sgrid, 256, 0, stream>>>((const bf*)x, xt, xg, (const bf*)w, bias, (bf*)y, (const bf*)gate, gate_t, M, G, N, K, act, vec);
     else
       return PTB_ERR_DTYPE;
     return launch_status();

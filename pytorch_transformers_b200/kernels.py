@@ -850,8 +850,12 @@ def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, n_g
         raise KernelError("route: the router's matrix and correction are float32 [outputs, width] and [outputs]")
     ids = torch.empty((n_tokens, top), dtype=torch.int32, device=h.device)
     gates = torch.empty((n_tokens, top), dtype=torch.float32, device=h.device)
-    _check(lib().ptb_route(_dtype_code(h), _ptr(h), _ptr(w_router), _ptr(correction), _ptr(ids), _ptr(gates), n_tokens,
-                           width, n, n_groups, keep, top, ctypes.c_float(scale), _stream(h)), "route")
+    logits = torch.empty((n_tokens, n), dtype=torch.float32, device=h.device)
+    _check(lib().ptb_route(_dtype_code(h), _ptr(h), _ptr(w_router), _ptr(correction), _ptr(logits), _ptr(ids),
+                           _ptr(gates), n_tokens, width, n, n_groups, keep, top, ctypes.c_float(scale), _stream(h)),
+           "route")
+    global launches
+    launches += 1       # the logits and the choice are two kernels
     return ids, gates
 
 
