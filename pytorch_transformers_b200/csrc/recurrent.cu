@@ -40,6 +40,14 @@ __global__ void rglru_conv_kernel(const T* __restrict__ proj, const float* __res
   }
 }
 
+// a S + drive with a = exp(log_a), formed as S + ((a - 1) S + drive) with a - 1 = expm1(log_a): a decay close
+// to 1 rounded to float32 is off by up to 3e-8 of itself, which a channel whose decay hardly changes would
+// carry into every step alike (1,000 steps: 3e-5 of the state); a - 1 keeps its digits, and what is left is
+// the rounding of the sum, which does not add up in one direction.
+__device__ __forceinline__ float decayed(float S, float log_a, float drive) {
+  return S + fmaf(expm1f(log_a), S, drive);
+}
+
 // One thread per (sequence, channel) walks the sequence's new tokens in order:
 //   log a = -c_decay * r * softplus(lam),  a = exp(log a)
 //   S <- a S + sqrt(1 - a^2) * (i * u),    out = S * y_act
@@ -66,9 +74,8 @@ __global__ void rglru_scan_kernel(const float* __restrict__ gates, const T* __re
     const size_t t = size_t(start + i);
     const float r = gates[t * 2 * R + goff], in = gates[t * 2 * R + goff + bw];
     const float log_a = -c_decay * r * sp;
-    const float a = expf(log_a);
     const float drive = sqrtf(-expm1f(2.f * log_a)) * (in * to_f(u[t * R + c]));
-    S = fmaf(a, S, drive);
+    S = decayed(S, log_a, drive);
     out[t * R + c] = from_f<T>(S * to_f(y_act[t * R + c]));
   }
   st[c] = S;
@@ -81,7 +88,8 @@ __global__ void rglru_scan_kernel(const float* __restrict__ gates, const T* __re
 }
 
 // The same recurrence for long prompts, cut into chunks of consecutive tokens of one sequence so that the
-// chunks run side by side: S_end = A S_start + B with A the product of a chunk's decays and B its result
+// chunks run side by side: S_end = A S_start + B with A the product of a chunk's decays (kept as the sum of
+// their logarithms) and B its result
 // from S_start = 0. Pass 1 (a thread per chunk and channel) finds (A, B) of every chunk; pass 2 (a thread
 // per sequence and channel) walks a sequence's chunks in order, notes every chunk's S_start, and leaves
 // the state (S and the convolution's last inputs); pass 3 (a thread per chunk and channel) runs the
@@ -105,7 +113,7 @@ __global__ void rglru_chunk_kernel(const float* __restrict__ gates, const T* __r
     const int first = seq_chunk0[seq], count = (n_new + chunk_len - 1) / chunk_len;
     for (int k = first; k < first + count; ++k) {
       s_start[size_t(k) * R + c] = S;
-      S = fmaf(agg_a[size_t(k) * R + c], S, agg_b[size_t(k) * R + c]);
+      S = decayed(S, agg_a[size_t(k) * R + c], agg_b[size_t(k) * R + c]);     // agg_a holds the chunk's summed log a
     }
     st[c] = S;
     float keep[MAX_TAPS];
@@ -122,14 +130,13 @@ __global__ void rglru_chunk_kernel(const float* __restrict__ gates, const T* __r
   const float l = lam[c];
   const float sp = (l > 20.f) ? l : log1pf(expf(l));
   const size_t goff = size_t(c / bw) * 2 * bw + c % bw;
-  float S = (PASS == 3) ? s_start[size_t(chunk) * R + c] : 0.f, A = 1.f;
+  float S = (PASS == 3) ? s_start[size_t(chunk) * R + c] : 0.f, A = 0.f;      // A: the chunk's summed log a
   for (int i = 0; i < count; ++i) {
     const size_t t = size_t(first + i);
     const float r = gates[t * 2 * R + goff], in = gates[t * 2 * R + goff + bw];
     const float log_a = -c_decay * r * sp;
-    const float a = expf(log_a);
-    S = fmaf(a, S, sqrtf(-expm1f(2.f * log_a)) * (in * to_f(u[t * R + c])));
-    if (PASS == 1) A *= a;
+    S = decayed(S, log_a, sqrtf(-expm1f(2.f * log_a)) * (in * to_f(u[t * R + c])));
+    if (PASS == 1) A += log_a;
     if (PASS == 3) out[t * R + c] = from_f<T>(S * to_f(y_act[t * R + c]));
   }
   if (PASS == 1) {

@@ -2,7 +2,7 @@
 
 The configurations differ from one another in every size: head counts, sizes that are no multiple of
 8, ranks, layer order, which layer reads whose cache entry, layers without a feed-forward, router
-shapes; "ones" sets to 1 what can be 1 (heads, blocks, taps, top, groups) and has no identity
+shapes; "recurrent" has no attention layer and "shared" three attention layers on one cache entry; "ones" sets to 1 what can be 1 (heads, blocks, taps, top, groups) and has no identity
 expert. Weights are drawn so that every tensor matters: norm gains around 1, router corrections
 large enough to change choices (and negative), decays spread over (0, 1).
 """
@@ -58,6 +58,18 @@ CONFIGS = {
         (latent(1, 16, 4, 16, 8, 8), moe(16, 2, 1)),
         (rglru(32, 1, 1), moe(16, 1, 1)),
     ], 1.0, 1e-6),
+    # no attention at all: no paged cache entry, state only
+    "recurrent": _cfg(50, 40, [
+        (rglru(48, 4, 2), moe(8, 2, 1, identity=1, count=1, keep=1, scale=1.0)),
+        (rglru(24, 2, 5), None),
+    ], 1.0, 1e-5),
+    # two later layers read the first layer's cache entry, one of them right after it
+    "shared": _cfg(80, 48, [
+        (latent(2, 8, 4, 12, 16, 24, base=300.0), None),
+        (latent(4, 6, 4, 8, 12, 24, base=300.0, kv_from=0), moe(12, 3, 2, identity=0, count=3, keep=2, scale=1.0)),
+        (rglru(32, 2, 3), None),
+        (latent(1, 20, 4, 24, 8, 24, base=300.0, kv_from=0, scale=0.3), None),
+    ], 0.7, 1e-6),
     # head size 64 + 16 and 16 heads, as a served model's shapes in small: vector loads and many head chunks
     "wide": _cfg(300, 256, [
         (latent(18, 32, 16, 32, 64, 64, base=1e6), moe(64, 8, 2, identity=0, count=2, keep=1, scale=1.5)),

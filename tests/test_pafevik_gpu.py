@@ -42,12 +42,13 @@ def row_errors(got, ref):
 
 def close(got, ref, dtype, what="", f32=2e-5, bf16=3e-2):
     """float32: every row within rounding of float32 sums. bfloat16: the rows' median within a bfloat16
-    model's rounding and nine rows in ten within twice that (a router's close call may move a row)."""
+    model's rounding and 85 rows in 100 within twice that: a router's close call moves a row, and through a
+    recurrence's state the few rows after it."""
     e = row_errors(got, ref)
     if dtype == "float32":
         assert e.max() < f32, f"{what}: worst row error {e.max():.3g}"
     else:
-        assert e.median() < bf16 and (e < 2 * bf16).double().mean() >= 0.9, \
+        assert e.median() < bf16 and (e < 2 * bf16).double().mean() >= 0.85, \
             f"{what}: median row error {e.median():.3g}, worst {e.max():.3g}"
 
 
@@ -288,7 +289,7 @@ def test_recurrence_keeps_a_slow_decay_exact():
     from pytorch_transformers_b200.cache.paged import Cache
     from pytorch_transformers_b200.engine.batch import StepContext
     from pytorch_transformers_b200.parts.base import StateNeed
-    R, T = 32, 50
+    R, T = 32, 1500      # a decay rounded to float32 and used 1,500 times alike would be off by 4e-5 of the state
     cache = Cache([(0, None, StateNeed(R))], 64, torch.float32, "cuda")
     slot = cache.open()
     ctx = StepContext(cache, [slot], [[0] * T], 1, [[]])
@@ -304,7 +305,7 @@ def test_recurrence_keeps_a_slow_decay_exact():
     for t in range(T):
         S = a * S + torch.sqrt(-torch.expm1(2 * log_a)) * u[t].double()
         rows.append(S.clone())
-    torch.testing.assert_close(out.double().cpu(), torch.stack(rows), atol=1e-6, rtol=2e-6)
+    torch.testing.assert_close(out.double().cpu(), torch.stack(rows), atol=2e-6, rtol=2e-6)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
