@@ -569,6 +569,7 @@ class KernelTimes:
     NAMES = ("gather_rows", "norm", "norm_stream", "add_stream", "residual", "bias_act_", "to_float", "matmul_nt",
              "skinny_linear", "linear_f32", "rope_table", "split_rotate_store", "attention_tc", "attention_mma",
              "attention_generic", "attention_decode", "attention_decode_tc", "latent_store", "latent_attention",
+             "latent_unfolded_attention",
              "latent_expand", "block_linear", "rglru_conv", "rglru_scan", "rglru_scan_chunks", "route", "routed_experts", "scale_")
 
     def __init__(self, kernels):
@@ -694,6 +695,13 @@ def run_pafevik(args):
     if t:
         roof["latent_attention_prefill_TFLOPs_as_run"] = round(H * tokens * (tokens + 1) / 2 * 2 * (dk + rank) / t / 1e9, 1)
         roof["latent_attention_prefill_frac_of_burst"] = round(roof["latent_attention_prefill_TFLOPs_as_run"] / pk["bf16_tflops"], 3)
+    t = per_call(P["prefill_kernels_ms"], "latent_unfolded_attention")
+    if t:   # gather, unfolding product, scatter, query layout, the tcgen05 kernel and the gate together
+        m0 = raw["layers"][0]["mixer"]
+        flops = H * tokens * (tokens + 1) / 2 * 2 * (m0["dim"] + m0["rot_dim"] + m0["vdim"]) + \
+            2 * tokens * rank * H * (m0["dim"] + m0["vdim"])
+        roof["latent_attention_prefill_unfolded_TFLOPs"] = round(flops / t / 1e9, 1)
+        roof["latent_attention_prefill_unfolded_frac_of_burst"] = round(flops / t / 1e9 / pk["bf16_tflops"], 3)
     t = per_call(F["prefill_kernels_ms"], "attention_tc")
     if t:
         roof["falcon_attention_prefill_TFLOPs"] = round(H * tokens * (tokens + 1) / 2 * 4 * 128 / t / 1e9, 1)

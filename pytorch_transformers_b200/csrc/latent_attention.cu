@@ -668,3 +668,127 @@ PTB_API int ptb_latent_attention_mma(const float* q_abs, const void* q, int q_di
   }
 #undef PTB_LMMA
 }
+
+// ------------------------------------------------------------------------------------------------
+// Prompts in bfloat16 with per-head sizes that the tcgen05 prompt kernel takes (csrc/attention_tc.cu: 64 or
+// 128): the cached latents of the step's sequences are unfolded into per-head keys [W_uk[h] c | kr | 0] and
+// values [W_uv[h] c | 0] in scratch pools laid out like a cache entry's ([pages][heads][64][hd], the same
+// page numbers), and that kernel runs on them. The pieces here: the context's cache rows gathered into
+// dense matrices (for the library's product with [W_uk; W_uv]), the product's rows scattered into the
+// pools, the queries laid out as [plain | rotated | 0], and the output gate on the heads' first vdim entries.
+namespace {
+
+__global__ void latent_gather_kernel(const __nv_bfloat16* __restrict__ pool, StepBatch sb,
+                                     const int* __restrict__ ctx_seq, const int* __restrict__ ctx_pos,
+                                     __nv_bfloat16* __restrict__ c_rows, __nv_bfloat16* __restrict__ kr_rows, int rank,
+                                     int rot_dim) {
+  const int i = blockIdx.x, seq = ctx_seq[i], pos = ctx_pos[i];
+  const int page = sb.pages[size_t(seq) * sb.pages_stride + pos / PTB_PAGE];
+  const __nv_bfloat16* src = pool + kv_offset(page, 0, pos % PTB_PAGE, 1, rank + rot_dim);
+  for (int e = threadIdx.x; e < rank; e += blockDim.x) c_rows[size_t(i) * rank + e] = src[e];
+  for (int e = threadIdx.x; e < rot_dim; e += blockDim.x) kr_rows[size_t(i) * rot_dim + e] = src[rank + e];
+}
+
+// kv [ctx, heads * dim + heads * vdim]: a context row's keys of all heads, then its values of all heads
+__global__ void latent_unfold_kernel(const __nv_bfloat16* __restrict__ kv, const __nv_bfloat16* __restrict__ kr_rows,
+                                     StepBatch sb, const int* __restrict__ ctx_seq, const int* __restrict__ ctx_pos,
+                                     __nv_bfloat16* __restrict__ k_tmp, __nv_bfloat16* __restrict__ v_tmp, int heads,
+                                     int dim, int rot_dim, int vdim, int hd) {
+  const int i = blockIdx.x, seq = ctx_seq[i], pos = ctx_pos[i];
+  const int page = sb.pages[size_t(seq) * sb.pages_stride + pos / PTB_PAGE], slot = pos % PTB_PAGE;
+  const size_t width = size_t(heads) * (dim + vdim);
+  const __nv_bfloat16* row = kv + size_t(i) * width;
+  const int dq = dim + rot_dim;
+  for (int idx = threadIdx.x; idx < heads * dq; idx += blockDim.x) {
+    const int h = idx / dq, e = idx % dq;
+    k_tmp[kv_offset(page, h, slot, heads, hd) + e] = (e < dim) ? row[size_t(h) * dim + e] : kr_rows[size_t(i) * rot_dim + (e - dim)];
+  }
+  for (int idx = threadIdx.x; idx < heads * vdim; idx += blockDim.x) {
+    const int h = idx / vdim, e = idx % vdim;
+    v_tmp[kv_offset(page, h, slot, heads, hd) + e] = row[size_t(heads) * dim + size_t(h) * vdim + e];
+  }
+}
+
+__global__ void latent_q_unfold_kernel(const __nv_bfloat16* __restrict__ q, const float* __restrict__ rope_cos,
+                                       const float* __restrict__ rope_sin, int rot_pairs, int interleaved,
+                                       __nv_bfloat16* __restrict__ out, int heads, int dim, int rot_dim, int hd) {
+  const size_t t = blockIdx.x;
+  const int dq = dim + rot_dim;
+  const int items = dim + rot_pairs + (rot_dim - 2 * rot_pairs) + (hd - dq);     // per head: plain, pairs, unrotated rest, padding
+  for (int idx = threadIdx.x; idx < heads * items; idx += blockDim.x) {
+    const int h = idx / items;
+    int e = idx % items;
+    const __nv_bfloat16* src = q + (t * heads + h) * dq;
+    __nv_bfloat16* dst = out + (t * heads + h) * hd;
+    if (e < dim) { dst[e] = src[e]; continue; }
+    e -= dim;
+    if (e < rot_pairs) {
+      const int ia = interleaved ? 2 * e : e, ib = interleaved ? 2 * e + 1 : e + rot_pairs;
+      float a, b;
+      rotate_pair(to_f(src[dim + ia]), to_f(src[dim + ib]), rope_cos[t * rot_pairs + e], rope_sin[t * rot_pairs + e], a, b);
+      dst[dim + ia] = __float2bfloat16_rn(a);
+      dst[dim + ib] = __float2bfloat16_rn(b);
+      continue;
+    }
+    e -= rot_pairs;
+    if (e < rot_dim - 2 * rot_pairs) { dst[dim + 2 * rot_pairs + e] = src[dim + 2 * rot_pairs + e]; continue; }
+    e -= rot_dim - 2 * rot_pairs;
+    dst[dq + e] = __float2bfloat16_rn(0.f);
+  }
+}
+
+// out[t, h, :vdim] = o[t, h, :vdim] * sigmoid(gate[t, h, :vdim]); o rows are hd wide
+__global__ void gate_heads_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ gate,
+                                  long long gate_t, __nv_bfloat16* __restrict__ out, long long total, int heads, int vdim,
+                                  int hd) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < size_t(total); i += stride) {
+    const int e = int(i % vdim), h = int((i / vdim) % heads);
+    const size_t t = i / (size_t(vdim) * heads);
+    const float g = to_f(gate[t * gate_t + size_t(h) * vdim + e]);
+    out[i] = __float2bfloat16_rn(to_f(o[(t * heads + h) * hd + e]) / (1.f + expf(-g)));
+  }
+}
+
+}  // namespace
+
+PTB_API int ptb_latent_gather(const void* pool, const StepBatch* sb, const int* ctx_seq, const int* ctx_pos, int n_ctx,
+                              void* c_rows, void* kr_rows, int rank, int rot_dim, cudaStream_t stream) {
+  if (n_ctx <= 0) return PTB_OK;
+  if (rank <= 0 || rot_dim < 0) return PTB_ERR_SIZE;
+  latent_gather_kernel<<<n_ctx, 128, 0, stream>>>((const __nv_bfloat16*)pool, *sb, ctx_seq, ctx_pos, (__nv_bfloat16*)c_rows,
+                                                  (__nv_bfloat16*)kr_rows, rank, rot_dim);
+  return launch_status();
+}
+
+PTB_API int ptb_latent_unfold(const void* kv, const void* kr_rows, const StepBatch* sb, const int* ctx_seq,
+                              const int* ctx_pos, int n_ctx, void* k_tmp, void* v_tmp, int heads, int dim, int rot_dim,
+                              int vdim, int hd, cudaStream_t stream) {
+  if (n_ctx <= 0) return PTB_OK;
+  if (heads <= 0 || dim <= 0 || rot_dim < 0 || vdim <= 0 || dim + rot_dim > hd || vdim > hd) return PTB_ERR_SIZE;
+  latent_unfold_kernel<<<n_ctx, 256, 0, stream>>>((const __nv_bfloat16*)kv, (const __nv_bfloat16*)kr_rows, *sb, ctx_seq,
+                                                  ctx_pos, (__nv_bfloat16*)k_tmp, (__nv_bfloat16*)v_tmp, heads, dim, rot_dim,
+                                                  vdim, hd);
+  return launch_status();
+}
+
+PTB_API int ptb_latent_q_unfold(const void* q, const float* rope_cos, const float* rope_sin, int rot_pairs,
+                                int interleaved, void* out, int n_tokens, int heads, int dim, int rot_dim, int hd,
+                                cudaStream_t stream) {
+  if (n_tokens <= 0) return PTB_OK;
+  if (heads <= 0 || dim <= 0 || rot_dim < 0 || dim + rot_dim > hd || 2 * rot_pairs > rot_dim) return PTB_ERR_SIZE;
+  if (rot_pairs > 0 && (rope_cos == nullptr || rope_sin == nullptr)) return PTB_ERR_SIZE;
+  latent_q_unfold_kernel<<<n_tokens, 256, 0, stream>>>((const __nv_bfloat16*)q, rope_cos, rope_sin, rot_pairs, interleaved,
+                                                       (__nv_bfloat16*)out, heads, dim, rot_dim, hd);
+  return launch_status();
+}
+
+PTB_API int ptb_gate_heads(const void* o, const void* gate, long long gate_t, void* out, int n_tokens, int heads, int vdim,
+                           int hd, cudaStream_t stream) {
+  const long long total = (long long)n_tokens * heads * vdim;
+  if (total <= 0) return PTB_OK;
+  const size_t want = (size_t(total) + 255) / 256, most = size_t(sm_count()) * 16;
+  gate_heads_kernel<<<int(want < most ? want : most), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)gate,
+                                                                       gate_t, (__nv_bfloat16*)out, total, heads, vdim, hd);
+  return launch_status();
+}

@@ -91,10 +91,11 @@ class CausalLM:
         self.planners, seen = [], set()
         for top in self._top_parts():
             for part in top.walk():
-                planner = part.planner()
-                if planner is not None and planner.plan_key not in seen:
-                    seen.add(planner.plan_key)
-                    self.planners.append(planner)
+                planner = part.planner()       # one planner, or several
+                for one in (planner if isinstance(planner, (list, tuple)) else [planner]):
+                    if one is not None and one.plan_key not in seen:
+                        seen.add(one.plan_key)
+                        self.planners.append(one)
         self._mixers = [b.children["mixer"] for b in self.blocks if "mixer" in b.children]
 
     def _top_parts(self) -> List[Part]:

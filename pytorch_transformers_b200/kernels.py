@@ -85,7 +85,8 @@ def lib():
                      "ptb_norm_stream", "ptb_add_stream", "ptb_latent_store", "ptb_latent_attention", "ptb_latent_rows",
                      "ptb_rglru_conv", "ptb_rglru_scan", "ptb_block_linear", "ptb_route", "ptb_expert_plan",
                      "ptb_expert_linear", "ptb_expert_combine", "ptb_expert_linear_mma", "ptb_latent_attention_mma",
-                     "ptb_latent_attention_mma_supports", "ptb_rglru_scan_chunks", "ptb_block_epilogue"):
+                     "ptb_latent_attention_mma_supports", "ptb_rglru_scan_chunks", "ptb_block_epilogue", "ptb_latent_gather",
+                     "ptb_latent_unfold", "ptb_latent_q_unfold", "ptb_gate_heads"):
             getattr(L, name).restype = ctypes.c_int
         L.ptb_latent_part_floats.restype = ctypes.c_longlong
         L.ptb_expert_plan_words.restype = ctypes.c_longlong
@@ -733,6 +734,41 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, q_rot_off: int, pool:
     if n_splits > 1:
         global launches
         launches += 1
+    return out
+
+
+def latent_unfolded_attention(q: torch.Tensor, pool: torch.Tensor, k_tmp: torch.Tensor, v_tmp: torch.Tensor,
+                              w_ukv: torch.Tensor, gate: torch.Tensor, batch: StepBatchC, ctx_seq: torch.Tensor,
+                              ctx_pos: torch.Tensor, n_ctx: int, mtile_seq: torch.Tensor, mtile_q0: torch.Tensor,
+                              n_mma_tiles: int, rope, dim: int, rot_dim: int, vdim: int, rank: int, scale: float,
+                              interleaved: bool = True) -> torch.Tensor:
+    """Latent attention of prompts through the tcgen05 prompt kernel (bfloat16): the ``n_ctx`` cached rows
+    (``ctx_seq``, ``ctx_pos``: sequence and position of each) of the step's sequences are unfolded with
+    ``w_ukv`` = [W_uk; W_uv] into per-head keys and values in the scratch pools ``k_tmp`` / ``v_tmp``
+    ([pages, heads, 64, hd], zero outside what is written here), the queries are laid out to match, and
+    ``attention_tc`` runs on them. Returns the heads' outputs times sigmoid(gate): [tokens, heads * vdim]."""
+    _need_cuda(q, pool, k_tmp, v_tmp, w_ukv, ctx_seq, ctx_pos)
+    n, heads, dq = q.shape
+    hd = k_tmp.shape[-1]
+    if q.dtype != torch.bfloat16 or dq != dim + rot_dim or tuple(w_ukv.shape) != (heads * (dim + vdim), rank):
+        raise KernelError("latent_unfolded_attention: sizes or dtypes do not fit")
+    cos, sin = rope if rope is not None else (None, None)
+    pairs = 0 if cos is None else cos.shape[1]
+    stream = _stream(q)
+    c_rows = torch.empty((n_ctx, rank), dtype=q.dtype, device=q.device)
+    kr_rows = torch.empty((n_ctx, max(rot_dim, 1)), dtype=q.dtype, device=q.device)
+    _check(lib().ptb_latent_gather(_ptr(pool), ctypes.byref(batch), _ptr(ctx_seq), _ptr(ctx_pos), n_ctx, _ptr(c_rows),
+                                   _ptr(kr_rows), rank, rot_dim, stream), "latent_gather")
+    kv = matmul_nt(c_rows, w_ukv)
+    _check(lib().ptb_latent_unfold(_ptr(kv), _ptr(kr_rows), ctypes.byref(batch), _ptr(ctx_seq), _ptr(ctx_pos), n_ctx,
+                                   _ptr(k_tmp), _ptr(v_tmp), heads, dim, rot_dim, vdim, hd, stream), "latent_unfold")
+    q_tc = torch.empty((n, heads, hd), dtype=q.dtype, device=q.device)
+    _check(lib().ptb_latent_q_unfold(_ptr(q), _ptr(cos), _ptr(sin), pairs, 1 if interleaved else 0, _ptr(q_tc), n, heads,
+                                     dim, rot_dim, hd, stream), "latent_q_unfold")
+    o = attention_tc(q_tc, k_tmp, v_tmp, batch, mtile_seq, mtile_q0, n_mma_tiles, heads, scale)
+    out = torch.empty((n, heads * vdim), dtype=q.dtype, device=q.device)
+    _check(lib().ptb_gate_heads(_ptr(o), _ptr(gate), ctypes.c_longlong(gate.stride(0)), _ptr(out), n, heads, vdim, hd,
+                                stream), "gate_heads")
     return out
 
 

@@ -197,8 +197,8 @@ class Part:
     def planner(self):
         """An object with ``plan_key`` (a string) and ``plan(ctx) -> engine.batch.StepPlan`` if this part's
         kernels need per-step integer arrays or numbers beyond the step's own (tile lists, say); parts
-        with the same ``plan_key`` share one plan per step, found as ``ctx.plan(plan_key)``. None: the part
-        needs nothing."""
+        with the same ``plan_key`` share one plan per step, found as ``ctx.plan(plan_key)``. A part may return
+        a list of such objects. None: the part needs nothing."""
         return None
 
     def runs_beside(self, ctx) -> bool:
