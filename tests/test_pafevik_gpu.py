@@ -393,6 +393,43 @@ def test_each_request_alone_and_whole(loaded, name, dtype):
     cache.check()
 
 
+@pytest.mark.parametrize("name", ["wide", "shared"])
+def test_long_prompts_unfolded_and_folded_agree(loaded, name):
+    """Long prompts of a bfloat16 model go through the tcgen05 prompt kernel on unfolded keys and values, also a
+    portion that continues cached tokens; with that path switched off the folded kernel gives the same rows."""
+    L = loaded(name, "bfloat16")
+    k = K()
+    ids = pm.prompts(L.cfg, (400,), seed=9)[0]
+    ref = L.plain_logits(ids)
+    calls, orig = [], k.latent_unfolded_attention
+
+    def spy(*a, **kw):
+        calls.append(1)
+        return orig(*a, **kw)
+
+    def run():
+        cache = L.model.new_cache(448)
+        s = cache.open()
+        return torch.cat([L.model.step(cache, [s], [ids[:300]], want="all"), L.model.step(cache, [s], [ids[300:]], want="all")])
+
+    layers = [m for m in L.model._mixers if hasattr(m, "_unfold_size")]
+    k.latent_unfolded_attention = spy
+    try:
+        unfolded = run()
+        assert len(calls) == 2 * len(layers)
+        for m in layers:
+            m._unfold_size = lambda: 0
+        folded = run()
+        assert len(calls) == 2 * len(layers)
+    finally:
+        k.latent_unfolded_attention = orig
+        for m in layers:
+            m.__dict__.pop("_unfold_size", None)
+    close(unfolded, ref, "bfloat16", f"{name} unfolded")
+    close(folded, ref, "bfloat16", f"{name} folded")
+    close(unfolded, folded, "bfloat16", f"{name} unfolded against folded")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_prompt_then_single_tokens(loaded, name, dtype):
