@@ -34,30 +34,46 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   __syncthreads();
   const __nv_bfloat16* we = w + size_t(expert) * (MODE == 0 ? 2 : 1) * N * K;
 
-  auto load_stage = [&](int stage, int k0) {
-    // A: 64 rows x 4 chunks; B: 128 rows x 4 chunks
-    for (int i = tid; i < GM * 4; i += GTHREADS) {
-      const int r = i / 4, c = i % 4, k = k0 + c * 8;
-      const uint32_t dst = smem_u32(a_s[stage]) + gswz(r, c);
-      const int sr = src_row[r];
-      if (sr >= 0 && k < K) cp_async16(dst, x + size_t(sr) * K + k);
-      else *reinterpret_cast<uint4*>(a_s[stage] + gswz(r, c)) = make_uint4(0, 0, 0, 0);
+  // what this thread copies in every stage: 2 chunks of the rows' tile and 4 of the matrix's, at fixed
+  // places; only k moves (addresses and bounds are worked out once, not in the loop)
+  const __nv_bfloat16* a_src[2];
+  uint32_t a_off[2];
+  const __nv_bfloat16* b_src[4];
+  uint32_t b_off[4];
+  const int kc = (tid % 4) * 8;       // this thread's chunk of a row: k0 + kc .. + 7
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int r = (tid + j * GTHREADS) / 4;
+    a_off[j] = gswz(r, tid % 4);
+    const int sr = src_row[r];
+    a_src[j] = sr >= 0 ? x + size_t(sr) * K + kc : nullptr;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int r = (tid + j * GTHREADS) / 4;
+    b_off[j] = gswz(r, tid % 4);
+    // row of the expert's matrix. mode 0: staged rows 64 nh + 32 part + cc hold column n0 + 32 nh + cc of the gate
+    // (part 0) or up (part 1) rows, so that a warp (one nh) has both for its 32 columns
+    int gn, col;
+    if (MODE == 0) {
+      col = n0 + (r >> 6) * 32 + (r & 31);
+      gn = ((r >> 5) & 1) ? N + col : col;
+    } else {
+      col = gn = n0 + r;
     }
-    for (int i = tid; i < GB * 4; i += GTHREADS) {
-      const int r = i / 4, c = i % 4, k = k0 + c * 8;
-      const uint32_t dst = smem_u32(b_s[stage]) + gswz(r, c);
-      // row of the expert's matrix. mode 0: staged rows 64 nh + 32 part + cc hold column n0 + 32 nh + cc of the gate
-      // (part 0) or up (part 1) rows, so that a warp (one nh) has both for its 32 columns
-      int gn, col;
-      if (MODE == 0) {
-        col = n0 + (r >> 6) * 32 + (r & 31);
-        gn = ((r >> 5) & 1) ? N + col : col;
-      } else {
-        col = gn = n0 + r;
-      }
-      const bool ok = col < N && k < K;
-      if (ok) cp_async16(dst, we + size_t(gn) * K + k);
-      else *reinterpret_cast<uint4*>(b_s[stage] + gswz(r, c)) = make_uint4(0, 0, 0, 0);
+    b_src[j] = col < N ? we + size_t(gn) * K + kc : nullptr;
+  }
+  auto load_stage = [&](int stage, int k0) {
+    const bool k_ok = k0 + kc < K;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      if (a_src[j] != nullptr && k_ok) cp_async16(smem_u32(a_s[stage]) + a_off[j], a_src[j] + k0);
+      else *reinterpret_cast<uint4*>(a_s[stage] + a_off[j]) = make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (b_src[j] != nullptr && k_ok) cp_async16(smem_u32(b_s[stage]) + b_off[j], b_src[j] + k0);
+      else *reinterpret_cast<uint4*>(b_s[stage] + b_off[j]) = make_uint4(0, 0, 0, 0);
     }
   };
 

@@ -70,11 +70,11 @@ CONFIGS = {
         (rglru(32, 2, 3), None),
         (latent(1, 20, 4, 24, 8, 24, base=300.0, kv_from=0, scale=0.3), None),
     ], 0.7, 1e-6),
-    # head size 64 + 16 and 16 heads, as a served model's shapes in small: vector loads and many head chunks
-    "wide": _cfg(300, 256, [
-        (latent(18, 32, 16, 32, 64, 64, base=1e6), moe(64, 8, 2, identity=0, count=2, keep=1, scale=1.5)),
-        (rglru(256, 4, 4), moe(64, 8, 2, identity=0, count=2, keep=1, scale=1.5)),
-    ], 0.5, 1e-6),
+    # 18 heads in two chunks of 16, tensor-core shapes (latent 128, rotated part 32), keys of 64 and values of 40
+    "wide": _cfg(300, 192, [
+        (latent(18, 32, 32, 40, 72, 128, base=5e5), moe(48, 10, 3, identity=0, count=5, keep=2, scale=1.2)),
+        (rglru(192, 6, 4), moe(48, 10, 3, identity=0, count=5, keep=2, scale=1.2)),
+    ], 0.8, 1e-5),
 }
 
 

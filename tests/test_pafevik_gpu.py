@@ -170,11 +170,11 @@ def latent_case(dtype, heads, rank, rot, pasts, news, needle=None, base=10000.0,
     return out.double().cpu(), torch.cat(refs)
 
 
-LATENT_TOL = {"float32": dict(atol=2e-5, rtol=1e-4), "bfloat16": dict(atol=2e-2, rtol=2e-2)}
+LATENT_TOL = {"float32": dict(atol=2e-5, rtol=1e-4), "bfloat16": dict(atol=3e-2, rtol=2e-2)}
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,rank,rot", [(3, 48, 8), (5, 22, 6), (1, 8, 0), (18, 64, 16), (2, 130, 4)])
+@pytest.mark.parametrize("heads,rank,rot", [(3, 48, 8), (5, 22, 6), (1, 8, 0), (18, 128, 32), (20, 64, 48), (2, 130, 4)])
 def test_latent_attention_prompts_chunks_and_single_tokens(dtype, heads, rank, rot):
     for pasts, news in [((0, 0, 0), (1, 5, 70)), ((63, 64, 65, 0), (1, 1, 1, 1)), ((130, 2), (3, 129)), ((200,), (1,))]:
         got, ref = latent_case(dtype, heads, rank, rot, pasts, news, seed=heads)
@@ -309,7 +309,7 @@ def test_recurrence_keeps_a_slow_decay_exact():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,identity,count,keep,top", [(8, 2, 4, 2, 3), (6, 0, 3, 1, 2), (1, 0, 1, 1, 1), (18, 2, 2, 1, 2),
+@pytest.mark.parametrize("n,identity,count,keep,top", [(8, 2, 4, 2, 3), (6, 0, 3, 1, 2), (1, 0, 1, 1, 1), (20, 4, 2, 1, 3),
                                                       (70, 5, 5, 2, 6), (256, 0, 8, 4, 8)])
 def test_router_and_experts(dtype, n, identity, count, keep, top):
     k = K()
