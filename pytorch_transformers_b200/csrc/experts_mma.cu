@@ -1,6 +1,6 @@
 // The experts' grouped matrix products in bfloat16 on the tensor cores (mma.m16n8k16, float32 sums):
-// the tiles of the plan that expert_plan_kernel makes (csrc/experts.cu), 64 sorted rows of one expert
-// each. A block of 4 warps takes one tile x 128 rows of the expert's matrix; a warp owns 32 rows of the
+// the tiles of the plan that expert_plan_kernel makes (csrc/experts.cu), 64 or 128 sorted rows of one expert
+// each. A block of 4 or 8 warps takes one tile x 128 rows of the expert's matrix; a warp owns 32 rows of the
 // tile and 64 of the 128 matrix rows. Operands come through a three-stage cp.async ring of [rows][32] tiles whose
 // 16-byte chunks are XOR-swizzled so that ldmatrix meets no bank twice.
 //   mode 0: x rows are gathered from h by token; the 128 matrix rows are 64 gate rows and the 64 up rows
@@ -11,22 +11,26 @@
 
 namespace {
 
-constexpr int GM = 64, GB = 128, GK = 32, STAGES = 3, GTHREADS = 128;
+constexpr int GB = 128, GK = 32, STAGES = 3;   // matrix rows of a block, step along K, stages of the ring
 
 // byte offset of 16-byte chunk c (0..3) of row r in a [rows][32] bfloat16 tile
 __device__ __forceinline__ uint32_t gswz(int r, int c) { return uint32_t(r * 64 + ((c ^ ((r >> 1) & 3)) << 4)); }
 
-template <int MODE>
-__global__ void __launch_bounds__(GTHREADS)
+// GM: rows of a tile (64: 4 warps, or 128: 8 warps, which halves the matrix's bytes per product where experts
+// have that many rows); a warp owns 32 rows x 64 staged matrix rows.
+template <int MODE, int GM>
+__global__ void __launch_bounds__(2 * GM)
 expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ out_v,
                          const int* __restrict__ plan, int pairs, int max_tiles, int top, int N, int K) {
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
   const int expert = plan[1 + tile], row0 = plan[1 + max_tiles + tile], rows = plan[1 + 2 * max_tiles + tile];
   const int* pair_of_row = plan + 1 + 3 * max_tiles + pairs;
-  __shared__ __align__(128) unsigned char a_s[STAGES][GM * 64];
-  __shared__ __align__(128) unsigned char b_s[STAGES][GB * 64];
-  __shared__ int src_row[GM];
+  constexpr int GTHREADS = 2 * GM, B_COPIES = GB * 4 / GTHREADS;
+  extern __shared__ __align__(128) unsigned char gsm[];
+  unsigned char (*a_s)[GM * 64] = reinterpret_cast<unsigned char (*)[GM * 64]>(gsm);
+  unsigned char (*b_s)[GB * 64] = reinterpret_cast<unsigned char (*)[GB * 64]>(gsm + STAGES * GM * 64);
+  int* src_row = reinterpret_cast<int*>(gsm + STAGES * (GM + GB) * 64);
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   constexpr int NOUT = MODE == 0 ? 64 : 128;     // output columns of a block
   const int n0 = blockIdx.x * NOUT;
@@ -34,12 +38,12 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   __syncthreads();
   const __nv_bfloat16* we = w + size_t(expert) * (MODE == 0 ? 2 : 1) * N * K;
 
-  // what this thread copies in every stage: 2 chunks of the rows' tile and 4 of the matrix's, at fixed
+  // what this thread copies in every stage: 2 chunks of the rows' tile and 4 or 2 of the matrix's, at fixed
   // places; only k moves (addresses and bounds are worked out once, not in the loop)
   const __nv_bfloat16* a_src[2];
   uint32_t a_off[2];
-  const __nv_bfloat16* b_src[4];
-  uint32_t b_off[4];
+  const __nv_bfloat16* b_src[B_COPIES];
+  uint32_t b_off[B_COPIES];
   const int kc = (tid % 4) * 8;       // this thread's chunk of a row: k0 + kc .. + 7
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
@@ -49,7 +53,7 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
     a_src[j] = sr >= 0 ? x + size_t(sr) * K + kc : nullptr;
   }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < B_COPIES; ++j) {
     const int r = (tid + j * GTHREADS) / 4;
     b_off[j] = gswz(r, tid % 4);
     // row of the expert's matrix. mode 0: staged rows 64 nh + 32 part + cc hold column n0 + 32 nh + cc of the gate
@@ -71,7 +75,7 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
       else *reinterpret_cast<uint4*>(a_s[stage] + a_off[j]) = make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < B_COPIES; ++j) {
       if (b_src[j] != nullptr && k_ok) cp_async16(smem_u32(b_s[stage]) + b_off[j], b_src[j] + k0);
       else *reinterpret_cast<uint4*>(b_s[stage] + b_off[j]) = make_uint4(0, 0, 0, 0);
     }
@@ -158,21 +162,37 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 }  // namespace
 
 // rows of a tile that this kernel takes (the plan must be made with it)
-PTB_API int ptb_expert_linear_mma_tile_rows() { return GM; }
+PTB_API int ptb_expert_linear_mma_tile_rows() { return 64; }
 
-PTB_API int ptb_expert_linear_mma(int mode, const void* x, const void* w, void* out, const int* plan, int pairs,
-                                  int max_tiles, int top, int N, int K, cudaStream_t stream) {
-  if (pairs <= 0 || max_tiles <= 0) return PTB_OK;
-  if (N <= 0 || K <= 0 || K % 8 != 0 || max_tiles > 65535 || top <= 0) return PTB_ERR_SIZE;
-  if (!aligned16(x) || !aligned16(w)) return PTB_ERR_ALIGN;
-  if (mode == 0) {
-    dim3 grid((N + 63) / 64, max_tiles);
-    expert_linear_mma_kernel<0><<<grid, GTHREADS, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, plan,
-                                                               pairs, max_tiles, top, N, K);
-  } else {
-    dim3 grid((N + 127) / 128, max_tiles);
-    expert_linear_mma_kernel<1><<<grid, GTHREADS, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, plan,
-                                                               pairs, max_tiles, top, N, K);
+namespace {
+template <int MODE, int GM>
+int launch_expert_mma(const void* x, const void* w, void* out, const int* plan, int pairs, int max_tiles, int top, int N,
+                      int K, cudaStream_t stream) {
+  const size_t smem = size_t(STAGES) * (GM + GB) * 64 + GM * sizeof(int);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(expert_linear_mma_kernel<MODE, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
+        cudaSuccess)
+      return PTB_ERR_LAUNCH;
+    configured = true;
   }
+  dim3 grid((N + (MODE == 0 ? 63 : 127)) / (MODE == 0 ? 64 : 128), max_tiles);
+  expert_linear_mma_kernel<MODE, GM><<<grid, 2 * GM, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out,
+                                                                      plan, pairs, max_tiles, top, N, K);
   return launch_status();
+}
+}  // namespace
+
+// `tile_rows`: 64 or 128, the rows of the plan's tiles
+PTB_API int ptb_expert_linear_mma(int mode, const void* x, const void* w, void* out, const int* plan, int pairs,
+                                  int max_tiles, int top, int N, int K, int tile_rows, cudaStream_t stream) {
+  if (pairs <= 0 || max_tiles <= 0) return PTB_OK;
+  if (N <= 0 || K <= 0 || K % 8 != 0 || max_tiles > 65535 || top <= 0 || (tile_rows != 64 && tile_rows != 128))
+    return PTB_ERR_SIZE;
+  if (!aligned16(x) || !aligned16(w)) return PTB_ERR_ALIGN;
+  if (mode == 0)
+    return tile_rows == 64 ? launch_expert_mma<0, 64>(x, w, out, plan, pairs, max_tiles, top, N, K, stream)
+                           : launch_expert_mma<0, 128>(x, w, out, plan, pairs, max_tiles, top, N, K, stream);
+  return tile_rows == 64 ? launch_expert_mma<1, 64>(x, w, out, plan, pairs, max_tiles, top, N, K, stream)
+                         : launch_expert_mma<1, 128>(x, w, out, plan, pairs, max_tiles, top, N, K, stream);
 }

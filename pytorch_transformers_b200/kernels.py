@@ -871,7 +871,7 @@ def rglru_scan_chunks(gates: torch.Tensor, u: torch.Tensor, y_act: torch.Tensor,
 # ------------------------------------------------------------------------------------------------
 # Routed experts
 EXPERT_TILE_ROWS = (16, 64)   # rows of a tile of the grouped products: few pairs, many pairs
-EXPERT_MMA_TILE_ROWS = 64     # ptb_expert_linear_mma_tile_rows()
+EXPERT_MMA_TILE_ROWS = (64, 128)   # rows of a tile of the tensor-core kernel
 
 
 def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, n_groups: int, keep: int, top: int,
@@ -896,7 +896,7 @@ def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, n_g
 
 
 def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_gate_up: torch.Tensor,
-                   w_down: torch.Tensor, base: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   w_down: torch.Tensor, base: Optional[torch.Tensor] = None, mma_tile_rows: int = 0) -> torch.Tensor:
     """base + sum over a token's choices of weight * expert(h): experts ``w_gate_up`` [E, 2 F, width]
     (gate rows, then up rows) and ``w_down`` [E, width, F] compute down(silu(gate h) * (up h)); an id >= E
     is an identity expert. Pairs are sorted by expert on the device and run as tiles of grouped
@@ -909,7 +909,14 @@ def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_ga
     pairs = n_tokens * top
     # bfloat16 with row sizes in whole 16-byte words: the tensor-core kernel (tiles of 64 rows); else float32 FMAs
     mma = h.dtype == torch.bfloat16 and width % 8 == 0 and f % 8 == 0
-    tile_rows = EXPERT_MMA_TILE_ROWS if mma else (EXPERT_TILE_ROWS[0] if pairs <= 8 * n_experts else EXPERT_TILE_ROWS[1])
+    if mma:
+        # tiles of 64 rows; 128 are built and tested too, but with about 200 rows an expert they were slower
+        # (3.8 against 3.3 ms for four layers of 12,288 pairs over 64 experts): half-empty last tiles, fewer blocks an SM
+        tile_rows = mma_tile_rows or EXPERT_MMA_TILE_ROWS[0]
+        if tile_rows not in EXPERT_MMA_TILE_ROWS:
+            raise KernelError(f"routed_experts: tiles of {EXPERT_MMA_TILE_ROWS} rows, got {tile_rows}")
+    else:
+        tile_rows = EXPERT_TILE_ROWS[0] if pairs <= 8 * n_experts else EXPERT_TILE_ROWS[1]
     max_tiles = pairs // tile_rows + min(pairs, n_experts)
     L = lib()
     plan = torch.empty(int(L.ptb_expert_plan_words(pairs, max_tiles)), dtype=torch.int32, device=h.device)
@@ -920,9 +927,9 @@ def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_ga
     y = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
     if mma:
         _check(L.ptb_expert_linear_mma(0, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
-                                       stream), "expert_linear_mma (gate, up)")
+                                       tile_rows, stream), "expert_linear_mma (gate, up)")
         _check(L.ptb_expert_linear_mma(1, _ptr(a), _ptr(w_down), _ptr(y), _ptr(plan), pairs, max_tiles, top, width, f,
-                                       stream), "expert_linear_mma (down)")
+                                       tile_rows, stream), "expert_linear_mma (down)")
     else:
         _check(L.ptb_expert_linear(code, 0, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
                                    tile_rows, stream), "expert_linear (gate, up)")

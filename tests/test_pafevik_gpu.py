@@ -346,6 +346,8 @@ def test_router_and_experts(dtype, n, identity, count, keep, top):
         if dtype == "bfloat16":           # a stream of the model dtype takes the sum in its own dtype
             out16 = k.routed_experts(h.cuda(), ids, weights, gate_up, down, base=base.bfloat16().cuda())
             assert out16.dtype == torch.bfloat16
+            wide = k.routed_experts(h.cuda(), ids, weights, gate_up, down, base=base.cuda(), mma_tile_rows=128)
+            assert row_errors(wide[same.cuda()], ref[same]).max() < 2e-2      # the tensor-core kernel's tiles of 128 rows
 
 
 # ------------------------------------------------------------------------------------------------ whole models
