@@ -131,17 +131,25 @@ __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __rest
 // q [n_tokens, heads, head_dim]; out [n_tokens, heads * head_dim].
 // score(q at position p, key at position j) = (q . k_j + alibi_h(j)) * scale for j <= p
 // (and j > p - window when window > 0); softmax over those keys in float32; out = sum p_j v_j.
+// Values may have a size of their own (v_dim; the V pool is [pages][kv_heads][PTB_PAGE][v_dim]).
+// With `sinks` [heads] the softmax's denominator also holds exp(sink_h): a term without key or value,
+// not scaled, counted once per row. With `gate` (row t, head h at gate[t * gate_stride + h]) the head's
+// output is multiplied by sigmoid(gate); `out_scale` multiplies everything. Output row t, head h starts
+// at out[t * out_stride + h * v_dim].
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                          T* __restrict__ out, StepBatch sb, const int* __restrict__ tile_seq,
                          const int* __restrict__ tile_q0, const float* __restrict__ alibi_slopes, int heads,
-                         int kv_heads, int head_dim, float scale, int window) {
+                         int kv_heads, int head_dim, float scale, int window, int v_dim,
+                         const float* __restrict__ sinks, const T* __restrict__ gate, int gate_stride, float out_scale,
+                         int out_stride) {
   extern __shared__ float smem[];
+  const int wide = max(head_dim, v_dim);
   float* qs = smem;                                 // [BQ][head_dim]
-  float* kv = qs + BQ * head_dim;                   // [PTB_PAGE][head_dim + 1], K then V
-  float* ps = kv + PTB_PAGE * (head_dim + 1);       // [BQ][PTB_PAGE]
-  const int kstride = head_dim + 1;
+  float* kv = qs + BQ * head_dim;                   // [PTB_PAGE][wide + 1], K then V
+  float* ps = kv + PTB_PAGE * (wide + 1);           // [BQ][PTB_PAGE]
+  const int kstride = head_dim + 1, vstride = v_dim + 1;
 
   const int tile = blockIdx.x, h = blockIdx.y;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
@@ -173,7 +181,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
     const int page = pages[kb];
     const int valid = min(PTB_PAGE, last_pos + 1 - kb * PTB_PAGE);  // keys of this block that exist
     const T* kp = k_pool + kv_offset(page, g, 0, kv_heads, head_dim);
-    const T* vp = v_pool + kv_offset(page, g, 0, kv_heads, head_dim);
+    const T* vp = v_pool + kv_offset(page, g, 0, kv_heads, v_dim);
     __syncthreads();  // previous block's V and ps are no longer read
     for (int i = tid; i < PTB_PAGE * head_dim; i += THREADS) {
       const int j = i / head_dim, e = i % head_dim;
@@ -224,30 +232,37 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
     l_run = l_run * corr + l_blk;
     m_run = m_new;
     __syncthreads();  // all scores of this block are written, K is no longer read
-    for (int i = tid; i < PTB_PAGE * head_dim; i += THREADS) {
-      const int j = i / head_dim, e = i % head_dim;
-      kv[j * kstride + e] = (j < valid) ? to_f(vp[i]) : 0.f;
+    for (int i = tid; i < PTB_PAGE * v_dim; i += THREADS) {
+      const int j = i / v_dim, e = i % v_dim;
+      kv[j * vstride + e] = (j < valid) ? to_f(vp[i]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < DPT; ++i) acc[i] *= corr;
     for (int j = 0; j < PTB_PAGE; ++j) {
       const float p = ps[r * PTB_PAGE + j];
-      const float* vr = kv + j * kstride;
+      const float* vr = kv + j * vstride;
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
         const int e = c + 8 * i;
-        if (e < head_dim) acc[i] = fmaf(p, vr[e], acc[i]);
+        if (e < v_dim) acc[i] = fmaf(p, vr[e], acc[i]);
       }
     }
   }
   if (r < rows) {
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    T* o = out + (size_t(start + q0 + r) * heads + h) * head_dim;
+    float keep = 1.f;      // what the keys' share of the denominator shrinks by when the sink raises the reference
+    if (sinks) {
+      const float sink = sinks[h], m_all = fmaxf(m_run, sink);
+      keep = (m_run == -INFINITY) ? 0.f : expf(m_run - m_all);
+      l_run = l_run * keep + expf(sink - m_all);
+    }
+    float inv = (l_run > 0.f ? 1.f / l_run : 0.f) * keep * out_scale;
+    if (gate) inv *= 1.f / (1.f + expf(-to_f(gate[size_t(start + q0 + r) * gate_stride + h])));
+    T* o = out + size_t(start + q0 + r) * out_stride + size_t(h) * v_dim;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
       const int e = c + 8 * i;
-      if (e < head_dim) o[e] = from_f<T>(acc[i] * inv);
+      if (e < v_dim) o[e] = from_f<T>(acc[i] * inv);
     }
   }
 }
@@ -255,8 +270,10 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
 template <typename T>
 int launch_attention(const void* q, const void* k_pool, const void* v_pool, void* out, const StepBatch& sb,
                      const int* tile_seq, const int* tile_q0, int n_tiles, const float* slopes, int heads,
-                     int kv_heads, int head_dim, float scale, int window, cudaStream_t stream) {
-  const size_t smem = sizeof(float) * (size_t(BQ) * head_dim + size_t(PTB_PAGE) * (head_dim + 1) + BQ * PTB_PAGE);
+                     int kv_heads, int head_dim, float scale, int window, int v_dim, const float* sinks, const void* gate,
+                     int gate_stride, float out_scale, int out_stride, cudaStream_t stream) {
+  const int wide = head_dim > v_dim ? head_dim : v_dim;
+  const size_t smem = sizeof(float) * (size_t(BQ) * head_dim + size_t(PTB_PAGE) * (wide + 1) + BQ * PTB_PAGE);
   static size_t configured = 48 * 1024;  // per element type: raised when a larger head size first comes
   if (smem > configured) {
     if (cudaFuncSetAttribute(attention_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) !=
@@ -267,7 +284,8 @@ int launch_attention(const void* q, const void* k_pool, const void* v_pool, void
   dim3 grid(n_tiles, heads);
   attention_generic_kernel<T><<<grid, THREADS, smem, stream>>>((const T*)q, (const T*)k_pool, (const T*)v_pool,
                                                                (T*)out, sb, tile_seq, tile_q0, slopes, heads, kv_heads,
-                                                               head_dim, scale, window);
+                                                               head_dim, scale, window, v_dim, sinks, (const T*)gate,
+                                                               gate_stride, out_scale, out_stride);
   return launch_status();
 }
 
@@ -318,16 +336,20 @@ PTB_API int ptb_split_rotate_store(int dtype, const void* fused, void* q_out, vo
 PTB_API int ptb_attention_generic(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,
                                   const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
                                   const float* alibi_slopes, int heads, int kv_heads, int head_dim, float scale,
-                                  int window, cudaStream_t stream) {
+                                  int window, int v_dim, const float* sinks, const void* gate, int gate_stride,
+                                  float out_scale, int out_stride, cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || head_dim <= 0 || head_dim > MAX_D || heads > 65535)
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || head_dim <= 0 || head_dim > MAX_D || heads > 65535 ||
+      v_dim <= 0 || v_dim > MAX_D || out_stride < heads * v_dim)
     return PTB_ERR_SIZE;
   if (dtype == PTB_F32)
     return launch_attention<float>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, alibi_slopes, heads,
-                                   kv_heads, head_dim, scale, window, stream);
+                                   kv_heads, head_dim, scale, window, v_dim, sinks, gate, gate_stride, out_scale, out_stride,
+                                   stream);
   if (dtype == PTB_BF16)
     return launch_attention<__nv_bfloat16>(q, k_pool, v_pool, out, *sb, tile_seq, tile_q0, n_tiles, alibi_slopes,
-                                           heads, kv_heads, head_dim, scale, window, stream);
+                                           heads, kv_heads, head_dim, scale, window, v_dim, sinks, gate, gate_stride,
+                                           out_scale, out_stride, stream);
   return PTB_ERR_DTYPE;
 }
 

@@ -518,3 +518,46 @@ PTB_API int ptb_to_float(int dtype, const void* x, float* out, long long total, 
     return PTB_ERR_DTYPE;
   return launch_status();
 }
+
+// x <- cap * tanh(x / cap), in place on float32 values (a soft limit on the logits)
+__global__ void softcap_kernel(float* __restrict__ x, float cap, size_t total) {
+  const size_t stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) x[i] = cap * tanhf(x[i] / cap);
+}
+
+PTB_API int ptb_softcap(float* x, float cap, long long total, cudaStream_t stream) {
+  if (total <= 0) return PTB_OK;
+  if (!(cap > 0.f)) return PTB_ERR_SIZE;
+  softcap_kernel<<<grid_for(size_t(total), 256), 256, 0, stream>>>(x, cap, size_t(total));
+  return launch_status();
+}
+
+// The clamped gated unit between a feed-forward's two products. in [rows, 2 F]: gate columns, then up columns;
+//     g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1)       [rows, F]
+// in float32 arithmetic, rounded once.
+template <typename T>
+__global__ void glu_clamp_kernel(const T* __restrict__ in, T* __restrict__ out, int rows, int f, float limit,
+                                 float alpha) {
+  const size_t total = size_t(rows) * f, stride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t r = i / f, c = i % f;
+    const float g = fminf(to_f(in[r * 2 * f + c]), limit);
+    const float u = fminf(fmaxf(to_f(in[r * 2 * f + f + c]), -limit), limit);
+    out[i] = from_f<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
+PTB_API int ptb_glu_clamp(int dtype, const void* in, void* out, int rows, int f, float limit, float alpha,
+                          cudaStream_t stream) {
+  if (rows <= 0) return PTB_OK;
+  if (f <= 0) return PTB_ERR_SIZE;
+  const int blocks = grid_for(size_t(rows) * f, 256);
+  if (dtype == PTB_F32)
+    glu_clamp_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, rows, f, limit, alpha);
+  else if (dtype == PTB_BF16)
+    glu_clamp_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, f,
+                                                                limit, alpha);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}

@@ -6,6 +6,7 @@
 // choice score, only the `keep` best groups stay eligible; the `top` largest eligible choice scores
 // are chosen (ties: lowest index); the weight of a chosen output is s * route_scale (not renormalised).
 // The last n - n_experts outputs are identity experts: they pass their input on.
+// score_kind 1: s = sigmoid(z) per output instead of the softmax. correction may be null (none).
 #include "common.cuh"
 
 namespace {
@@ -49,7 +50,7 @@ route_logits_kernel(const T* __restrict__ h, const float* __restrict__ w_router,
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 route_select_kernel(const float* __restrict__ zs_all, const float* __restrict__ correction, int* __restrict__ ids,
                     float* __restrict__ gates, int n_tokens, int n, int n_groups, int keep, int top,
-                    float route_scale) {
+                    float route_scale, int score_kind) {
   extern __shared__ float sm[];   // per warp: n choice scores, n_groups group scores
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t = blockIdx.x * ROUTE_WARPS + warp;
@@ -77,8 +78,9 @@ route_select_kernel(const float* __restrict__ zs_all, const float* __restrict__ 
 #pragma unroll
   for (int v = 0; v < ROUTE_VPL; ++v) {
     const int e = lane + 32 * v;
-    s[v] = s[v] / sum;
-    if (e < n) choice[e] = s[v] + correction[e];
+    if (score_kind == 1) s[v] = (e < n) ? 1.f / (1.f + expf(-z[v])) : 0.f;
+    else s[v] = s[v] / sum;
+    if (e < n) choice[e] = s[v] + (correction ? correction[e] : 0.f);
   }
   __syncwarp();
   const int per = n / n_groups;
@@ -199,6 +201,9 @@ expert_plan_kernel(const int* __restrict__ ids, int* __restrict__ plan, int pair
 // Grouped product over the plan's tiles. MODE 0: rows are gathered from h by token (pair / top),
 // W [experts, 2 F, K] holds gate rows then up rows, out[row, f] = silu(gate) * up in the model dtype.
 // MODE 1: rows are `x`'s sorted rows [pairs, K], W [experts, N, K], out [pairs, N] float32.
+// MODE 2: rows gathered from h as in MODE 0, W [experts, N, K] (an expert without a gate),
+// out[row, n] = act(row_scale[pair] * (W h)) in the model dtype: the expert's first product of the pair's
+// weight times the token's row (the weight commutes with the product).
 // float32 FMAs in ascending k (16 products summed apart, then into the total): a row's result does
 // not depend on its tile. A block computes TM * 16 rows x 64 outputs.
 constexpr int EBN = 64, EBK = 16, ETN = 4;
@@ -206,7 +211,8 @@ constexpr int EBN = 64, EBK = 16, ETN = 4;
 template <typename T, typename TO, int MODE, int TM>
 __global__ void __launch_bounds__(256)
 expert_linear_kernel(const T* __restrict__ x, const T* __restrict__ w, TO* __restrict__ out,
-                     const int* __restrict__ plan, int pairs, int max_tiles, int top, int N, int K) {
+                     const int* __restrict__ plan, int pairs, int max_tiles, int top, int N, int K,
+                     const float* __restrict__ row_scale, int act) {
   constexpr int EBM = TM * 16;
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
@@ -218,7 +224,7 @@ expert_linear_kernel(const T* __restrict__ x, const T* __restrict__ w, TO* __res
   const int tid = threadIdx.x;
   const int n0 = blockIdx.x * EBN;
   const int tm = (tid / 16) * TM, tn = (tid % 16) * ETN;
-  if (tid < EBM) src_row[tid] = (tid < rows) ? (MODE == 0 ? pair_of_row[row0 + tid] / top : row0 + tid) : -1;
+  if (tid < EBM) src_row[tid] = (tid < rows) ? (MODE != 1 ? pair_of_row[row0 + tid] / top : row0 + tid) : -1;
   __syncthreads();
   const T* we = w + size_t(expert) * (MODE == 0 ? 2 : 1) * N * K;
   float acc[MODE == 0 ? 2 : 1][TM][ETN];
@@ -277,13 +283,15 @@ expert_linear_kernel(const T* __restrict__ x, const T* __restrict__ w, TO* __res
       if (gn >= N) continue;
       float v = acc[0][i][j];
       if (MODE == 0) v = v / (1.f + expf(-v)) * acc[MODE == 0 ? 1 : 0][i][j];
+      if (MODE == 2) v = apply_activation(v * (row_scale ? row_scale[pair_of_row[row0 + tm + i]] : 1.f), act);
       out[size_t(row0 + tm + i) * N + gn] = from_f<TO>(v);
     }
   }
 }
 
 // out[t] = base[t] + sum_k gate[t, k] * (expert output row of the pair, or h[t] for an identity expert),
-// summed in float32 in the order of the choice; base and out are float32 or of the model dtype (TB).
+// summed in float32 in the order of the choice (gate null: every weight is one); base and out are float32 or of
+// the model dtype (TB).
 // One block per token.
 template <typename T, typename TB>
 __global__ void expert_combine_kernel(const TB* __restrict__ base, const T* __restrict__ h,
@@ -296,7 +304,7 @@ __global__ void expert_combine_kernel(const TB* __restrict__ base, const T* __re
     for (int k = 0; k < top; ++k) {
       const int row = row_of_pair[size_t(t) * top + k];
       const float v = (row >= 0) ? y[size_t(row) * width + i] : to_f(h[size_t(t) * width + i]);
-      s = fmaf(gates[size_t(t) * top + k], v, s);
+      s = fmaf(gates ? gates[size_t(t) * top + k] : 1.f, v, s);
     }
     out[size_t(t) * width + i] = from_f<TB>((base ? to_f(base[size_t(t) * width + i]) : 0.f) + s);
   }
@@ -304,14 +312,14 @@ __global__ void expert_combine_kernel(const TB* __restrict__ base, const T* __re
 
 template <typename T, typename TO, int MODE>
 int launch_expert_linear(const void* x, const void* w, void* out, const int* plan, int pairs, int max_tiles, int top,
-                         int N, int K, int tile_rows, cudaStream_t stream) {
+                         int N, int K, int tile_rows, const float* row_scale, int act, cudaStream_t stream) {
   dim3 grid((N + EBN - 1) / EBN, max_tiles);
   if (tile_rows == 16)
     expert_linear_kernel<T, TO, MODE, 1><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, (TO*)out, plan, pairs,
-                                                                   max_tiles, top, N, K);
+                                                                   max_tiles, top, N, K, row_scale, act);
   else if (tile_rows == 64)
     expert_linear_kernel<T, TO, MODE, 4><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, (TO*)out, plan, pairs,
-                                                                   max_tiles, top, N, K);
+                                                                   max_tiles, top, N, K, row_scale, act);
   else
     return PTB_ERR_SIZE;
   return launch_status();
@@ -322,10 +330,10 @@ int launch_expert_linear(const void* x, const void* w, void* out, const int* pla
 // `logits`: float32 scratch [n_tokens, n]
 PTB_API int ptb_route(int dtype, const void* h, const float* w_router, const float* correction, float* logits, int* ids,
                       float* gates, int n_tokens, int width, int n, int n_groups, int keep, int top, float route_scale,
-                      cudaStream_t stream) {
+                      int score_kind, cudaStream_t stream) {
   if (n_tokens <= 0) return PTB_OK;
   if (n <= 0 || n > 32 * ROUTE_VPL || n_groups <= 0 || n % n_groups != 0 || keep <= 0 || keep > n_groups || top <= 0 ||
-      top > (n / n_groups) * keep || width <= 0)
+      top > (n / n_groups) * keep || width <= 0 || score_kind < 0 || score_kind > 1)
     return PTB_ERR_SIZE;
   // few tokens (steps of single tokens): one token a block, so that the blocks fill the device
   const int tpb = n_tokens >= 2 * sm_count() ? ROUTE_TOKENS : 1;
@@ -345,7 +353,7 @@ PTB_API int ptb_route(int dtype, const void* h, const float* w_router, const flo
   if (launch_status() != PTB_OK) return PTB_ERR_LAUNCH;
   const size_t smem = size_t(ROUTE_WARPS) * (n + n_groups) * sizeof(float);
   route_select_kernel<<<(n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, 32 * ROUTE_WARPS, smem, stream>>>(
-      logits, correction, ids, gates, n_tokens, n, n_groups, keep, top, route_scale);
+      logits, correction, ids, gates, n_tokens, n, n_groups, keep, top, route_scale, score_kind);
   return launch_status();
 }
 
@@ -362,19 +370,21 @@ PTB_API int ptb_expert_plan(const int* ids, int* plan, int pairs, int n_experts,
   return launch_status();
 }
 
-// mode 0: gate and up with silu(gate) * up, out in the model dtype; mode 1: down, out float32
+// mode 0: gate and up with silu(gate) * up, out in the model dtype; mode 1: down, out float32; mode 2: one product
+// with act(row_scale * .), out in the model dtype (row_scale [pairs] float32 or null, act: an activation code)
 PTB_API int ptb_expert_linear(int dtype, int mode, const void* x, const void* w, void* out, const int* plan, int pairs,
-                              int max_tiles, int top, int N, int K, int tile_rows, cudaStream_t stream) {
+                              int max_tiles, int top, int N, int K, int tile_rows, const float* row_scale, int act,
+                              cudaStream_t stream) {
   if (pairs <= 0 || max_tiles <= 0) return PTB_OK;
-  if (N <= 0 || K <= 0 || max_tiles > 65535 || top <= 0) return PTB_ERR_SIZE;
-  if (dtype == PTB_F32)
-    return mode == 0 ? launch_expert_linear<float, float, 0>(x, w, out, plan, pairs, max_tiles, top, N, K, tile_rows, stream)
-                     : launch_expert_linear<float, float, 1>(x, w, out, plan, pairs, max_tiles, top, N, K, tile_rows, stream);
+  if (N <= 0 || K <= 0 || max_tiles > 65535 || top <= 0 || mode < 0 || mode > 2 || !activation_known(act))
+    return PTB_ERR_SIZE;
+#define PTB_EL(TT, TTO, MM) \
+  launch_expert_linear<TT, TTO, MM>(x, w, out, plan, pairs, max_tiles, top, N, K, tile_rows, row_scale, act, stream)
+  if (dtype == PTB_F32) return mode == 0 ? PTB_EL(float, float, 0) : mode == 1 ? PTB_EL(float, float, 1) : PTB_EL(float, float, 2);
   if (dtype == PTB_BF16)
-    return mode == 0 ? launch_expert_linear<__nv_bfloat16, __nv_bfloat16, 0>(x, w, out, plan, pairs, max_tiles, top, N,
-                                                                             K, tile_rows, stream)
-                     : launch_expert_linear<__nv_bfloat16, float, 1>(x, w, out, plan, pairs, max_tiles, top, N, K,
-                                                                     tile_rows, stream);
+    return mode == 0 ? PTB_EL(__nv_bfloat16, __nv_bfloat16, 0)
+                     : mode == 1 ? PTB_EL(__nv_bfloat16, float, 1) : PTB_EL(__nv_bfloat16, __nv_bfloat16, 2);
+#undef PTB_EL
   return PTB_ERR_DTYPE;
 }
 

@@ -6,6 +6,8 @@
 //   mode 0: x rows are gathered from h by token; the 128 matrix rows are 64 gate rows and the 64 up rows
 //           of the same columns; out[row, f] = silu(gate) * up, bfloat16.
 //   mode 1: x rows are the sorted rows themselves; out[row, n] float32.
+//   mode 2: x rows gathered as in mode 0, 128 plain matrix rows; out[row, n] = act(row_scale[pair] * sum), bfloat16
+//           (an expert without a gate whose input is the token's row times the pair's weight).
 // A row's sums do not depend on its place in a tile or on the other rows.
 #include "mma_common.cuh"
 
@@ -21,7 +23,8 @@ __device__ __forceinline__ uint32_t gswz(int r, int c) { return uint32_t(r * 64 
 template <int MODE, int GM>
 __global__ void __launch_bounds__(2 * GM)
 expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ out_v,
-                         const int* __restrict__ plan, int pairs, int max_tiles, int top, int N, int K) {
+                         const int* __restrict__ plan, int pairs, int max_tiles, int top, int N, int K,
+                         const float* __restrict__ row_scale, int act) {
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
   const int expert = plan[1 + tile], row0 = plan[1 + max_tiles + tile], rows = plan[1 + 2 * max_tiles + tile];
@@ -34,7 +37,7 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   constexpr int NOUT = MODE == 0 ? 64 : 128;     // output columns of a block
   const int n0 = blockIdx.x * NOUT;
-  if (tid < GM) src_row[tid] = (tid < rows) ? (MODE == 0 ? pair_of_row[row0 + tid] / top : row0 + tid) : -1;
+  if (tid < GM) src_row[tid] = (tid < rows) ? (MODE != 1 ? pair_of_row[row0 + tid] / top : row0 + tid) : -1;
   __syncthreads();
   const __nv_bfloat16* we = w + size_t(expert) * (MODE == 0 ? 2 : 1) * N * K;
 
@@ -144,6 +147,17 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
             o[col] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
           }
         }
+      } else if (MODE == 2) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_v) + size_t(row0 + r) * N;
+        const float rs = row_scale ? row_scale[pair_of_row[row0 + r]] : 1.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int col = n0 + wn * 64 + j * 8 + c0 + q;
+            if (col < N) o[col] = __float2bfloat16_rn(apply_activation(acc[mi][j][half * 2 + q] * rs, act));
+          }
+        }
       } else {
         float* o = reinterpret_cast<float*>(out_v) + size_t(row0 + r) * N;
 #pragma unroll
@@ -167,7 +181,7 @@ PTB_API int ptb_expert_linear_mma_tile_rows() { return 64; }
 namespace {
 template <int MODE, int GM>
 int launch_expert_mma(const void* x, const void* w, void* out, const int* plan, int pairs, int max_tiles, int top, int N,
-                      int K, cudaStream_t stream) {
+                      int K, const float* row_scale, int act, cudaStream_t stream) {
   const size_t smem = size_t(STAGES) * (GM + GB) * 64 + GM * sizeof(int);
   static bool configured = false;
   if (!configured) {
@@ -178,21 +192,23 @@ int launch_expert_mma(const void* x, const void* w, void* out, const int* plan, 
   }
   dim3 grid((N + (MODE == 0 ? 63 : 127)) / (MODE == 0 ? 64 : 128), max_tiles);
   expert_linear_mma_kernel<MODE, GM><<<grid, 2 * GM, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out,
-                                                                      plan, pairs, max_tiles, top, N, K);
+                                                                      plan, pairs, max_tiles, top, N, K, row_scale, act);
   return launch_status();
 }
 }  // namespace
 
 // `tile_rows`: 64 or 128, the rows of the plan's tiles
 PTB_API int ptb_expert_linear_mma(int mode, const void* x, const void* w, void* out, const int* plan, int pairs,
-                                  int max_tiles, int top, int N, int K, int tile_rows, cudaStream_t stream) {
+                                  int max_tiles, int top, int N, int K, int tile_rows, const float* row_scale, int act,
+                                  cudaStream_t stream) {
   if (pairs <= 0 || max_tiles <= 0) return PTB_OK;
-  if (N <= 0 || K <= 0 || K % 8 != 0 || max_tiles > 65535 || top <= 0 || (tile_rows != 64 && tile_rows != 128))
+  if (N <= 0 || K <= 0 || K % 8 != 0 || max_tiles > 65535 || top <= 0 || (tile_rows != 64 && tile_rows != 128) ||
+      mode < 0 || mode > 2 || !activation_known(act))
     return PTB_ERR_SIZE;
   if (!aligned16(x) || !aligned16(w)) return PTB_ERR_ALIGN;
-  if (mode == 0)
-    return tile_rows == 64 ? launch_expert_mma<0, 64>(x, w, out, plan, pairs, max_tiles, top, N, K, stream)
-                           : launch_expert_mma<0, 128>(x, w, out, plan, pairs, max_tiles, top, N, K, stream);
-  return tile_rows == 64 ? launch_expert_mma<1, 64>(x, w, out, plan, pairs, max_tiles, top, N, K, stream)
-                         : launch_expert_mma<1, 128>(x, w, out, plan, pairs, max_tiles, top, N, K, stream);
+#define PTB_EM(MM, GG) launch_expert_mma<MM, GG>(x, w, out, plan, pairs, max_tiles, top, N, K, row_scale, act, stream)
+  if (mode == 0) return tile_rows == 64 ? PTB_EM(0, 64) : PTB_EM(0, 128);
+  if (mode == 2) return tile_rows == 64 ? PTB_EM(2, 64) : PTB_EM(2, 128);
+  return tile_rows == 64 ? PTB_EM(1, 64) : PTB_EM(1, 128);
+#undef PTB_EM
 }

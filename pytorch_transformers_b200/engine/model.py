@@ -81,6 +81,9 @@ class CausalLM:
                 raise ValueError(f"schedule entry reads cache entry {e.cache_entry}, which no entry writes")
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
+        self.position_table: Optional[torch.Tensor] = None
+        if spec.position_table_name is not None and not (spec.stream_float32 and spec.max_positions > 0):
+            raise ValueError("a learned position table needs a float32 stream and max_positions > 0")
         self.status = None  # device int32 word raised by kernels that clamp a bad index
         # replay steps of single tokens as CUDA graphs, if every part allows it
         self.use_graphs = all(p.graph_safe for top in self._top_parts() for p in top.walk())
@@ -109,6 +112,8 @@ class CausalLM:
         table[self.spec.embedding_name] = (None, "embedding", ParamDecl((v, h)))
         if self.spec.head_name is not None:
             table[self.spec.head_name] = (None, "head", ParamDecl((v, h)))
+        if self.spec.position_table_name is not None:
+            table[self.spec.position_table_name] = (None, "positions", ParamDecl((self.spec.max_positions, h)))
         for top in self._top_parts():
             for part in top.walk():
                 for logical, decl in part.param_decls().items():
@@ -137,19 +142,25 @@ class CausalLM:
             if part is None:
                 if logical == "embedding":
                     self.embedding = t
+                elif logical == "positions":
+                    self.position_table = t
                 else:
                     self.head = t
             else:
                 per_part.setdefault(id(part), (part, {}))[1][logical] = t
         for part, group in per_part.values():
             part.bind(group)
+        for top in self._top_parts():       # parts that put their children's tensors together (one product for two mixers)
+            for part in top.walk():
+                if hasattr(part, "after_bind"):
+                    part.after_bind()
         if self.spec.head_name is None:
             self.head = self.embedding  # one device buffer for the gather and the output product
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
-        tensors = [self.embedding, self.head]
+        tensors = [self.embedding, self.head, self.position_table]
         for top in self._top_parts():
             for part in top.walk():
                 tensors += [getattr(part, a) for a in vars(part) if a.startswith("p_")]
@@ -227,6 +238,11 @@ class CausalLM:
                 want = [[] for _ in token_lists]
             else:
                 raise StepError(f"want must be 'last', 'all', 'none' or lists of positions, got {want!r}")
+        if self.position_table is not None:
+            for s, t in zip(slots, token_lists):
+                if cache.length(s) + len(t) > self.spec.max_positions:
+                    raise StepError(f"the model has learned vectors for {self.spec.max_positions} positions; the sequence in "
+                                    f"slot {s} would reach {cache.length(s) + len(t)} tokens")
         single = all(len(t) == 1 for t in token_lists) and all(list(w) == [0] for w in want)
         ctx = self._take_prepared(cache, slots)     # whatever was prepared is used now or never
         if single and self.use_graphs and self.device.type == "cuda":
@@ -361,7 +377,11 @@ class CausalLM:
             if self._side_stream is None:
                 self._side_stream = torch.cuda.Stream(device=self.device)
             ctx.side_stream = self._side_stream
-        x = k.gather_rows(ctx.dev["tokens"], self.embedding, self.status)
+        if self.position_table is not None:
+            # embeddings plus the positions' learned vectors, straight into the float32 stream
+            x = k.embed_sum(ctx.dev["tokens"], ctx.dev["tok_pos"], self.embedding, self.position_table, self.status)
+        else:
+            x = k.gather_rows(ctx.dev["tokens"], self.embedding, self.status)
         if self.spec.embedding_scale != 1.0:
             k.scale_(x, self.spec.embedding_scale)
         if self.embedding_norm is not None:
@@ -389,4 +409,6 @@ class CausalLM:
             out = k.matmul_nt(rows, self.head, out_dtype=torch.float32)
         if self.spec.logit_scale != 1.0:
             k.scale_(out, self.spec.logit_scale)
+        if self.spec.logit_softcap > 0.0:
+            k.softcap_(out, self.spec.logit_softcap)
         return out

@@ -67,6 +67,14 @@ def _need_cuda(*tensors) -> None:
             raise KernelError("kernels take contiguous tensors")
 
 
+def _check_rows(t: torch.Tensor, shape, dtype, what: str) -> None:
+    """``t`` is a CUDA tensor [rows, n] of ``dtype`` whose rows are contiguous (the rows themselves may lie wider apart:
+    a slice of columns of a wider tensor)."""
+    if not t.is_cuda or tuple(t.shape) != tuple(shape) or t.dtype != dtype or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{what} must be a CUDA tensor {tuple(shape)} of {dtype} with contiguous rows, got "
+                          f"{tuple(t.shape)} of {t.dtype}, strides {t.stride()}")
+
+
 _configured = False
 
 
@@ -86,7 +94,9 @@ def lib():
                      "ptb_rglru_conv", "ptb_rglru_scan", "ptb_block_linear", "ptb_route", "ptb_expert_plan",
                      "ptb_expert_linear", "ptb_expert_combine", "ptb_expert_linear_mma", "ptb_latent_attention_mma",
                      "ptb_latent_attention_mma_supports", "ptb_rglru_scan_chunks", "ptb_block_epilogue", "ptb_latent_gather",
-                     "ptb_latent_unfold", "ptb_latent_q_unfold", "ptb_gate_heads"):
+                     "ptb_latent_unfold", "ptb_latent_q_unfold", "ptb_gate_heads", "ptb_linear_attention_scan",
+                     "ptb_linear_attention_chunks", "ptb_linear_attention_chunks_supports", "ptb_norm_gate",
+                     "ptb_qk_norm_store", "ptb_post_norm_add", "ptb_embed_sum", "ptb_softcap", "ptb_glu_clamp"):
             getattr(L, name).restype = ctypes.c_int
         L.ptb_latent_part_floats.restype = ctypes.c_longlong
         L.ptb_expert_plan_words.restype = ctypes.c_longlong
@@ -227,14 +237,26 @@ def split_rotate_store(fused: torch.Tensor, k_pool: Optional[torch.Tensor], v_po
 
 def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC,
                       tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
-                      slopes: Optional[torch.Tensor], kv_heads: int, scale: float, window: int = 0) -> torch.Tensor:
-    """Causal attention of the step's tokens over the paged cache; returns [tokens, heads * head_dim]."""
-    _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes)
+                      slopes: Optional[torch.Tensor], kv_heads: int, scale: float, window: int = 0,
+                      sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, out_scale: float = 1.0,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of the step's tokens over the paged cache; returns [tokens, heads * v_dim] (v_dim is
+    the V pool's row size). ``sinks`` [heads] float32: a term exp(sink) in every row's softmax denominator
+    that has no key and no value. ``gate`` [tokens, heads] (a view whose rows may be wider apart): each head's
+    output times sigmoid(gate). ``out``: a [tokens, heads * v_dim] view (rows may be wider apart) to write into."""
+    _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes, sinks)
     n, heads, head_dim = q.shape
-    out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
+    v_dim = v_pool.shape[-1]
+    if out is None:
+        out = torch.empty((n, heads * v_dim), dtype=q.dtype, device=q.device)
+    _check_rows(out, (n, heads * v_dim), q.dtype, "attention_generic: out")
+    if gate is not None:
+        _check_rows(gate, (n, heads), q.dtype, "attention_generic: gate")
     _check(lib().ptb_attention_generic(_dtype_code(q), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out),
                                        ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
-                                       heads, kv_heads, head_dim, ctypes.c_float(scale), window, _stream(q)),
+                                       heads, kv_heads, head_dim, ctypes.c_float(scale), window, v_dim, _ptr(sinks),
+                                       _ptr(gate), 0 if gate is None else gate.stride(0), ctypes.c_float(out_scale),
+                                       out.stride(0), _stream(q)),
            "attention_generic")
     return out
 
@@ -874,21 +896,26 @@ EXPERT_TILE_ROWS = (16, 64)   # rows of a tile of the grouped products: few pair
 EXPERT_MMA_TILE_ROWS = (64, 128)   # rows of a tile of the tensor-core kernel
 
 
-def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, n_groups: int, keep: int, top: int,
-          scale: float):
-    """Router of a mixture of experts, float32: softmax over all outputs, choice by score + correction
-    among the ``keep`` best of ``n_groups`` groups, weights = score * scale. Returns (ids int32
-    [tokens, top], weights float32 [tokens, top])."""
+ROUTE_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], n_groups: int, keep: int, top: int,
+          scale: float, score: str = "softmax"):
+    """Router of a mixture of experts, float32: scores = softmax over all outputs (or a sigmoid per output),
+    choice by score + correction (None: no correction) among the ``keep`` best of ``n_groups`` groups,
+    weights = score * scale. Returns (ids int32 [tokens, top], weights float32 [tokens, top])."""
     _need_cuda(h, w_router, correction)
     n_tokens, width = h.shape
     n = w_router.shape[0]
-    if w_router.dtype != torch.float32 or correction.dtype != torch.float32 or w_router.shape[1] != width:
+    if (w_router.dtype != torch.float32 or (correction is not None and correction.dtype != torch.float32)
+            or w_router.shape[1] != width):
         raise KernelError("route: the router's matrix and correction are float32 [outputs, width] and [outputs]")
     ids = torch.empty((n_tokens, top), dtype=torch.int32, device=h.device)
     gates = torch.empty((n_tokens, top), dtype=torch.float32, device=h.device)
     logits = torch.empty((n_tokens, n), dtype=torch.float32, device=h.device)
     _check(lib().ptb_route(_dtype_code(h), _ptr(h), _ptr(w_router), _ptr(correction), _ptr(logits), _ptr(ids),
-                           _ptr(gates), n_tokens, width, n, n_groups, keep, top, ctypes.c_float(scale), _stream(h)),
+                           _ptr(gates), n_tokens, width, n, n_groups, keep, top, ctypes.c_float(scale),
+                           ROUTE_SCORES[score], _stream(h)),
            "route")
     global launches
     launches += 1       # the logits and the choice are two kernels
@@ -896,16 +923,22 @@ def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, n_g
 
 
 def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_gate_up: torch.Tensor,
-                   w_down: torch.Tensor, base: Optional[torch.Tensor] = None, mma_tile_rows: int = 0) -> torch.Tensor:
+                   w_down: torch.Tensor, base: Optional[torch.Tensor] = None, mma_tile_rows: int = 0,
+                   plain_act: Optional[str] = None) -> torch.Tensor:
     """base + sum over a token's choices of weight * expert(h): experts ``w_gate_up`` [E, 2 F, width]
     (gate rows, then up rows) and ``w_down`` [E, width, F] compute down(silu(gate h) * (up h)); an id >= E
     is an identity expert. Pairs are sorted by expert on the device and run as tiles of grouped
-    products. Returns [tokens, width] in ``base``'s dtype (float32 without a base)."""
+    products. Returns [tokens, width] in ``base``'s dtype (float32 without a base).
+
+    With ``plain_act`` (an activation's name) the experts have no gate and take their weight on the input:
+    ``w_gate_up`` is [E, F, width] and the result is base + sum of down(act(up (weight * h)))."""
     _need_cuda(h, ids, gates, w_gate_up, w_down, base)
     n_tokens, width = h.shape
     top = ids.shape[1]
     n_experts, two_f, _ = w_gate_up.shape
-    f = two_f // 2
+    f = two_f // 2 if plain_act is None else two_f
+    first, act = (0, 0) if plain_act is None else (2, ACTIVATIONS[plain_act])
+    scale = None if plain_act is None else gates
     pairs = n_tokens * top
     # bfloat16 with row sizes in whole 16-byte words: the tensor-core kernel (tiles of 64 rows); else float32 FMAs
     mma = h.dtype == torch.bfloat16 and width % 8 == 0 and f % 8 == 0
@@ -926,19 +959,147 @@ def routed_experts(h: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, w_ga
     a = torch.empty((pairs, f), dtype=h.dtype, device=h.device)
     y = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
     if mma:
-        _check(L.ptb_expert_linear_mma(0, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
-                                       tile_rows, stream), "expert_linear_mma (gate, up)")
+        _check(L.ptb_expert_linear_mma(first, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
+                                       tile_rows, _ptr(scale), act, stream), "expert_linear_mma (gate, up)")
         _check(L.ptb_expert_linear_mma(1, _ptr(a), _ptr(w_down), _ptr(y), _ptr(plan), pairs, max_tiles, top, width, f,
-                                       tile_rows, stream), "expert_linear_mma (down)")
+                                       tile_rows, None, 0, stream), "expert_linear_mma (down)")
     else:
-        _check(L.ptb_expert_linear(code, 0, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
-                                   tile_rows, stream), "expert_linear (gate, up)")
+        _check(L.ptb_expert_linear(code, first, _ptr(h), _ptr(w_gate_up), _ptr(a), _ptr(plan), pairs, max_tiles, top, f, width,
+                                   tile_rows, _ptr(scale), act, stream), "expert_linear (gate, up)")
         _check(L.ptb_expert_linear(code, 1, _ptr(a), _ptr(w_down), _ptr(y), _ptr(plan), pairs, max_tiles, top, width, f,
-                                   tile_rows, stream), "expert_linear (down)")
+                                   tile_rows, None, 0, stream), "expert_linear (down)")
     if base is not None and (base.shape != h.shape or base.dtype not in (torch.float32, h.dtype)):
         raise KernelError("routed_experts: base must have the input's shape, in float32 or the input's dtype")
     out = torch.empty((n_tokens, width), dtype=torch.float32 if base is None else base.dtype, device=h.device)
     row_of_pair = plan[1 + 3 * max_tiles:1 + 3 * max_tiles + pairs]
-    _check(L.ptb_expert_combine(code, _dtype_code(out), _ptr(base), _ptr(h), _ptr(y), _ptr(ids), _ptr(gates),
+    _check(L.ptb_expert_combine(code, _dtype_code(out), _ptr(base), _ptr(h), _ptr(y), _ptr(ids),
+                                _ptr(gates if plain_act is None else None),
                                 _ptr(row_of_pair), _ptr(out), n_tokens, width, top, stream), "expert_combine")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Linear attention with a fixed decay per head; norms and gates around mixers; the clamped gated unit
+LINEAR_ATTENTION_CHUNK = 64   # ptb_linear_attention_chunk_tokens()
+
+
+def linear_attention_chunks_supports(dim: int, v_dim: int) -> bool:
+    return bool(lib().ptb_linear_attention_chunks_supports(dim, v_dim))
+
+
+def linear_attention(proj: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, batch: StepBatchC, decay: torch.Tensor,
+                     heads: int, dim: int, v_dim: int, act: str = "silu", chunks=None) -> torch.Tensor:
+    """Per head S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over the step's tokens, continuing and leaving
+    each sequence's S [heads, dim, v_dim] in ``state`` [slots, heads * dim * v_dim] (float32; rows may lie wider
+    apart). ``proj`` [tokens, >= 2 heads dim + heads v_dim] holds q, k, v side by side (rows may lie wider apart);
+    ``act`` "silu" is applied to all three as they are read. ``chunks``: (chunk_seq, chunk_q0, seq_chunk0, n_chunks)
+    for the chunked form (prompts), None for the token-by-token form. Returns float32 [tokens, heads * v_dim]."""
+    _need_cuda(decay, slots)
+    n = proj.shape[0]
+    if state.dtype != torch.float32 or state.shape[1] != heads * dim * v_dim or state.stride(1) != 1:
+        raise KernelError("linear_attention: the state is float32 [slots, heads * dim * v_dim]")
+    _check_rows(proj, proj.shape, proj.dtype, "linear_attention: proj")
+    if act not in ("none", "silu") or decay.dtype != torch.float32 or decay.numel() != heads:
+        raise KernelError("linear_attention: act is 'none' or 'silu'; decay is float32 [heads]")
+    out = torch.empty((n, heads * v_dim), dtype=torch.float32, device=proj.device)
+    code, a = _dtype_code(proj), 1 if act == "silu" else 0
+    if chunks is None:
+        _check(lib().ptb_linear_attention_scan(code, _ptr(proj), proj.stride(0), _ptr(state), state.stride(0), _ptr(slots),
+                                               ctypes.byref(batch), _ptr(decay), _ptr(out), heads, dim, v_dim, a,
+                                               _stream(proj)), "linear_attention_scan")
+        return out
+    chunk_seq, chunk_q0, seq_chunk0, n_chunks = chunks
+    sums = torch.empty((n_chunks, heads, dim, v_dim), dtype=torch.float32, device=proj.device)
+    _check(lib().ptb_linear_attention_chunks(code, _ptr(proj), proj.stride(0), _ptr(state), state.stride(0), _ptr(slots),
+                                             ctypes.byref(batch), _ptr(chunk_seq), _ptr(chunk_q0), _ptr(seq_chunk0),
+                                             n_chunks, _ptr(decay), _ptr(sums), _ptr(out), heads, dim, v_dim, a,
+                                             _stream(proj)), "linear_attention_chunks")
+    global launches
+    launches += 2       # three kernels
+    return out
+
+
+def norm_gate(x: torch.Tensor, gain: torch.Tensor, gate: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+              out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMS norm of float32 rows ``x`` times ``gain`` times sigmoid(``gate``) times ``out_scale``, in ``out_dtype``.
+    ``gate`` and ``out`` [rows, width] are of ``out_dtype``; their rows may lie wider apart."""
+    _need_cuda(x, gain)
+    n, width = x.shape
+    if x.dtype != torch.float32:
+        raise KernelError("norm_gate takes float32 rows")
+    if out is None:
+        out = torch.empty((n, width), dtype=out_dtype, device=x.device)
+    _check_rows(out, (n, width), out_dtype, "norm_gate: out")
+    if gate is not None:
+        _check_rows(gate, (n, width), out_dtype, "norm_gate: gate")
+    _check(lib().ptb_norm_gate(_ptr(x), _ptr(gain), _dtype_code(out), _ptr(gate), 0 if gate is None else gate.stride(0),
+                               _dtype_code(out), _ptr(out), out.stride(0), n, width, ctypes.c_float(eps),
+                               ctypes.c_float(out_scale), _stream(x)), "norm_gate")
+    return out
+
+
+def qk_norm_store(proj: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC,
+                  q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int,
+                  v_dim: int, eps: float, write_cache: bool = True) -> torch.Tensor:
+    """``proj`` [tokens, >= (heads + kv_heads) dim + kv_heads v_dim] holds q, k, v side by side (rows may lie wider
+    apart). Queries and keys are RMS-normed per head with the gains [dim] (None: as they are); keys and values go
+    into the paged pools at the tokens' positions. Returns q [tokens, heads, dim]."""
+    _need_cuda(k_pool, v_pool, q_gain, k_gain)
+    _check_rows(proj, proj.shape, proj.dtype, "qk_norm_store: proj")
+    q = torch.empty((proj.shape[0], heads, dim), dtype=proj.dtype, device=proj.device)
+    _check(lib().ptb_qk_norm_store(_dtype_code(proj), _ptr(proj), proj.stride(0), _ptr(q), _ptr(k_pool), _ptr(v_pool),
+                                   ctypes.byref(batch), _ptr(q_gain), _ptr(k_gain), heads, kv_heads, dim, v_dim,
+                                   ctypes.c_float(eps), 1 if write_cache else 0, _stream(proj)), "qk_norm_store")
+    return q
+
+
+def post_norm_add(x: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float, mult: float,
+                  gain_next: Optional[torch.Tensor] = None, eps_next: float = 0.0,
+                  next_dtype: Optional[torch.dtype] = None):
+    """The float32 stream ``x`` plus ``mult`` times the RMS norm (gain ``gain``) of a branch's result ``y``
+    (float32 or bfloat16). With ``gain_next`` also the RMS norm of the new stream in ``next_dtype``:
+    returns ``out`` or ``(out, next)``."""
+    _need_cuda(x, y, gain, gain_next)
+    if x.dtype != torch.float32 or x.shape != y.shape:
+        raise KernelError("post_norm_add takes a float32 stream and a branch result of its shape")
+    n, width = x.shape
+    out = torch.empty_like(x)
+    nxt = torch.empty((n, width), dtype=next_dtype, device=x.device) if gain_next is not None else None
+    _check(lib().ptb_post_norm_add(_ptr(x), _dtype_code(y), _ptr(y), _ptr(gain), ctypes.c_float(eps), ctypes.c_float(mult),
+                                   _ptr(out), _ptr(gain_next), ctypes.c_float(eps_next),
+                                   0 if nxt is None else _dtype_code(nxt), _ptr(nxt), n, width, _stream(x)),
+           "post_norm_add")
+    return out if nxt is None else (out, nxt)
+
+
+def embed_sum(ids: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
+              status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 rows table[ids] + positions[pos]: token embeddings plus a learned vector per position."""
+    _need_cuda(ids, pos, table, positions)
+    if table.dtype != positions.dtype or table.shape[1] != positions.shape[1]:
+        raise KernelError("embed_sum: the two tables have one dtype and one width")
+    n, width = ids.numel(), table.shape[1]
+    out = torch.empty((n, width), dtype=torch.float32, device=table.device)
+    _check(lib().ptb_embed_sum(_dtype_code(table), _ptr(ids), _ptr(pos), _ptr(table), _ptr(positions), _ptr(out), n, width,
+                               table.shape[0], positions.shape[0], _ptr(status), _stream(table)), "embed_sum")
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _need_cuda(x)
+    if x.dtype != torch.float32:
+        raise KernelError("softcap_ takes float32 values")
+    _check(lib().ptb_softcap(_ptr(x), ctypes.c_float(cap), ctypes.c_longlong(x.numel()), _stream(x)), "softcap")
+    return x
+
+
+def glu_clamp(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """[rows, 2 F] (gate columns, then up columns) -> [rows, F]: g = min(gate, limit), u = clamp(up, -limit, limit),
+    g * sigmoid(alpha g) * (u + 1)."""
+    _need_cuda(gate_up)
+    rows, two_f = gate_up.shape
+    out = torch.empty((rows, two_f // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib().ptb_glu_clamp(_dtype_code(gate_up), _ptr(gate_up), _ptr(out), rows, two_f // 2, ctypes.c_float(limit),
+                               ctypes.c_float(alpha), _stream(gate_up)), "glu_clamp")
     return out

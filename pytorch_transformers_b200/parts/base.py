@@ -110,6 +110,12 @@ class ModelSpec:
     # the residual stream between the blocks is float32 whatever the model dtype (a bfloat16 model then
     # rounds only what enters a matrix product); False: the stream has the model dtype
     stream_float32: bool = False
+    # a learned vector per position, added to the embeddings: the checkpoint name of a table
+    # [max_positions, hidden] (None: no such table); needs a float32 stream
+    position_table_name: Optional[str] = None
+    max_positions: int = 0
+    # logits <- cap * tanh(logits / cap) after the head (0: none)
+    logit_softcap: float = 0.0
 
     def resolved_schedule(self) -> List[ScheduleEntry]:
         if self.schedule is not None:

@@ -103,3 +103,40 @@ class SequentialBlock(Part):
         if self.feed_forward is None:
             return r
         return _plus(k, self.feed_forward, r, self.norm_ff.forward(r), ctx)
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Part):
+    """A norm before and after each sublayer, and a fixed multiplier on what a sublayer adds:
+
+        x <- x + mult * post_mixer(mixer(norm_mixer(x)));      x <- x + mult * post_ff(ff(norm_ff(x)))
+
+    on a float32 residual stream (``ModelSpec.stream_float32``). All four norms are RMS norms. The closing norm of
+    the mixer's result, the stream's sum and the feed-forward's opening norm are one kernel; so are the closing norm
+    of the feed-forward's result and the sum. A block without ``feed_forward`` ends after its first half."""
+    graph_safe = True
+
+    def __init__(self, build: BuildContext, spec: PartSpec, mult: float = 1.0):
+        super().__init__(build, spec)
+        self.mult = float(mult)
+        self.norm_mixer, self.post_mixer, self.mixer = (self.children[n] for n in ("norm_mixer", "post_mixer", "mixer"))
+        self.feed_forward = self.children.get("feed_forward")
+        self.norm_ff = self.children["norm_ff"] if self.feed_forward is not None else None
+        self.post_ff = self.children["post_ff"] if self.feed_forward is not None else None
+        for n in (self.norm_mixer, self.post_mixer, self.norm_ff, self.post_ff):
+            if n is not None and (getattr(n, "kind", None) != "rmsnorm" or n.has_bias):
+                raise ValueError("the sandwich block's norms are RMS norms without bias")
+
+    def forward(self, x, ctx, entry):
+        import torch
+        k = self.build.kernels
+        x = resolve(k, x)
+        if x.dtype != torch.float32:
+            raise ValueError("the sandwich block runs on a float32 residual stream")
+        y = self.mixer.forward(self.norm_mixer.forward(x), ctx, entry)
+        if self.feed_forward is None:
+            return k.post_norm_add(x, y, self.post_mixer.p_weight, self.post_mixer.eps, self.mult)
+        x, h = k.post_norm_add(x, y, self.post_mixer.p_weight, self.post_mixer.eps, self.mult,
+                               gain_next=self.norm_ff.p_weight, eps_next=self.norm_ff.eps, next_dtype=self.build.dtype)
+        y = self.feed_forward.forward(h, ctx)
+        return k.post_norm_add(x, y, self.post_ff.p_weight, self.post_ff.eps, self.mult)

@@ -7,6 +7,11 @@ choice scores are chosen; a chosen output weighs ``s * scale`` (no renormalisati
 ``W_down (silu(W_gate h) * (W_up h))``; the last ``identity`` outputs are identity experts that pass
 ``h`` on and have no tensors. The result is the weighted sum over the chosen, added to the residual
 stream in float32 in the same kernel.
+
+Variants, all by constructor parameters: ``score="sigmoid"`` scores every output by a sigmoid of its own
+instead of the softmax; ``correction=False`` has no correction tensor; ``expert="plain"`` experts have no
+gate, ``W_down act(W_up h)`` with ``activation`` by name; ``weight_on="input"`` multiplies the expert's
+input by the weight instead of its output: the result is the sum of ``expert(weight * h)``.
 """
 from __future__ import annotations
 
@@ -23,8 +28,20 @@ class RoutedExperts(Part):
     fuses_add = True
 
     def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, inner: int, experts: int, top: int,
-                 identity: int = 0, groups: int = 1, keep: int = 1, scale: float = 1.0):
+                 identity: int = 0, groups: int = 1, keep: int = 1, scale: float = 1.0, score: str = "softmax",
+                 correction: bool = True, expert: str = "gated_silu", activation: str = "gelu",
+                 weight_on: str = "output"):
         super().__init__(build, spec)
+        if score not in build.kernels.ROUTE_SCORES:
+            raise ValueError(f"router scores are one of {', '.join(build.kernels.ROUTE_SCORES)}, got {score!r}")
+        if expert not in ("gated_silu", "plain") or weight_on not in ("output", "input"):
+            raise ValueError(f"experts are 'gated_silu' or 'plain' and weigh their 'output' or 'input', got {expert!r}, {weight_on!r}")
+        if (expert == "plain") != (weight_on == "input"):
+            # the grouped kernels take the weight in the plain expert's first epilogue, or in the sum of outputs
+            raise ValueError("plain experts weigh their input and gated experts their output")
+        if expert == "plain" and (activation not in build.kernels.ACTIVATIONS or identity):
+            raise ValueError(f"plain experts take an activation of {', '.join(build.kernels.ACTIVATIONS)} and no identity experts")
+        self.score, self.has_correction, self.expert, self.activation = score, bool(correction), expert, activation
         self.hidden, self.inner, self.experts, self.top = int(hidden), int(inner), int(experts), int(top)
         self.identity, self.groups, self.keep, self.scale = int(identity), int(groups), int(keep), float(scale)
         n = self.experts + self.identity
@@ -38,16 +55,23 @@ class RoutedExperts(Part):
 
     def param_decls(self) -> Dict[str, ParamDecl]:
         n = self.experts + self.identity
-        d = {"router": ParamDecl((n, self.hidden), role="vector"), "correction": ParamDecl((n,), role="vector")}
+        d = {"router": ParamDecl((n, self.hidden), role="vector")}
+        if self.has_correction:
+            d["correction"] = ParamDecl((n,), role="vector")
         for e in range(self.experts):
-            d[f"e{e}.gate"] = ParamDecl((self.inner, self.hidden))
+            if self.expert == "gated_silu":
+                d[f"e{e}.gate"] = ParamDecl((self.inner, self.hidden))
             d[f"e{e}.up"] = ParamDecl((self.inner, self.hidden))
             d[f"e{e}.down"] = ParamDecl((self.hidden, self.inner))
         return d
 
     def bind(self, t: Dict[str, torch.Tensor]) -> None:
-        self.p_router, self.p_correction = t["router"].contiguous(), t["correction"]
+        self.p_router, self.p_correction = t["router"].contiguous(), t.get("correction")
         E, F = self.experts, self.inner
+        if self.expert == "plain":      # [E, F, hidden] and [E, hidden, F]
+            self.p_gate_up = torch.stack([t.pop(f"e{e}.up") for e in range(E)]).contiguous()
+            self.p_down = torch.stack([t.pop(f"e{e}.down") for e in range(E)]).contiguous()
+            return
         # all experts in two tensors for the grouped products: [E, 2 F, hidden] (gate rows, then up rows), [E, hidden, F]
         gate_up = torch.empty((E, 2 * F, self.hidden), dtype=t["e0.gate"].dtype, device=t["e0.gate"].device)
         down = torch.empty((E, self.hidden, F), dtype=gate_up.dtype, device=gate_up.device)
@@ -61,5 +85,7 @@ class RoutedExperts(Part):
         k = self.build.kernels
         if callable(add):
             add = add()
-        ids, weights = k.route(x, self.p_router, self.p_correction, self.groups, self.keep, self.top, self.scale)
-        return k.routed_experts(x, ids, weights, self.p_gate_up, self.p_down, base=add)
+        ids, weights = k.route(x, self.p_router, self.p_correction, self.groups, self.keep, self.top, self.scale,
+                               self.score)
+        return k.routed_experts(x, ids, weights, self.p_gate_up, self.p_down, base=add,
+                                plain_act=self.activation if self.expert == "plain" else None)

@@ -36,3 +36,37 @@ class DenseFeedForward(Part):
         if callable(add):
             add = add()   # resolved as late as possible: the caller may still be producing it on another stream
         return linear(k, u, self.p_down_weight, self.p_down_bias, add=add)
+
+
+@register_part("feed_forward", "clamped_glu")
+class ClampedGatedFeedForward(Part):
+    """A gated feed-forward with clamped branches:
+
+        g = min(W_gate x, limit),  u = clamp(W_up x, -limit, limit),  y = W_down (g * sigmoid(alpha g) * (u + 1)).
+
+    Gate and up are one matrix and one product; the unit between the products is one kernel. ``forward``
+    returns the last product's float32 sums unrounded when asked (``wide_out``), for a norm that follows."""
+    graph_safe = True
+
+    def __init__(self, build: BuildContext, spec: PartSpec, hidden: int, inner: int, limit: float, alpha: float = 1.702,
+                 wide_out: bool = False):
+        super().__init__(build, spec)
+        self.hidden, self.inner, self.limit, self.alpha = int(hidden), int(inner), float(limit), float(alpha)
+        self.wide_out = bool(wide_out)
+        if not self.limit > 0:
+            raise ValueError(f"the clamp's limit must be positive, got {limit}")
+        self.p_gate_up = self.p_down = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {"gate": ParamDecl((self.inner, self.hidden)), "up": ParamDecl((self.inner, self.hidden)),
+                "down": ParamDecl((self.hidden, self.inner))}
+
+    def bind(self, t) -> None:
+        import torch
+        self.p_gate_up = torch.cat([t["gate"], t["up"]]).contiguous()
+        self.p_down = t["down"]
+
+    def forward(self, x, ctx):
+        k = self.build.kernels
+        y = k.glu_clamp(linear(k, x, self.p_gate_up), self.limit, self.alpha)
+        return linear(k, y, self.p_down, wide_out=self.wide_out)

@@ -24,8 +24,16 @@ TC_LINEAR_ROWS = None
 
 
 def linear(kernels, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           act: str = "none", add: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """act(x @ weight.T + bias) + add, in the model dtype; ``add`` has the result's shape."""
+           act: str = "none", add: Optional[torch.Tensor] = None, wide_out: bool = False) -> torch.Tensor:
+    """act(x @ weight.T + bias) + add, in the model dtype; ``add`` has the result's shape. ``wide_out``: a plain
+    product (no bias, activation or addend) whose float32 sums are returned unrounded (for a float32 norm or
+    sum that follows)."""
+    if wide_out and weight.dtype != torch.float32:
+        if bias is not None or act != "none" or add is not None:
+            raise ValueError("linear: wide_out is for a plain product")
+        if kernels.skinny_linear_preferred(x.shape[0], x.shape[1], weight.shape[0]):
+            return kernels.skinny_linear(x, weight, out_dtype=torch.float32)
+        return kernels.matmul_nt(x, weight, out_dtype=torch.float32)
     if weight.dtype == torch.float32:
         y = kernels.linear_f32(x, weight, bias, act)
         return y if add is None else kernels.residual(add, y)

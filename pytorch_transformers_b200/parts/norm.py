@@ -64,5 +64,19 @@ class LayerNorm(Part):
 class RMSNorm(LayerNorm):
     kind = "rmsnorm"
 
-    def __init__(self, build: BuildContext, spec: PartSpec, size: int, eps: float, bias: bool = False):
+    def __init__(self, build: BuildContext, spec: PartSpec, size: int, eps: float, bias: bool = False,
+                 one_plus: bool = False):
         super().__init__(build, spec, size, eps, bias)
+        # the stored weight is the gain's distance from one: y = x / rms(x) * (1 + w). The device holds 1 + w (float32).
+        self.one_plus = bool(one_plus)
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        d = super().param_decls()
+        if self.one_plus:
+            d["weight"] = ParamDecl((self.size,), role="vector", init="normal", std=0.1)
+        return d
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        if self.one_plus:
+            self.p_weight = self.p_weight + 1.0
