@@ -570,7 +570,8 @@ class KernelTimes:
              "skinny_linear", "linear_f32", "rope_table", "split_rotate_store", "attention_tc", "attention_mma",
              "attention_generic", "attention_decode", "attention_decode_tc", "latent_store", "latent_attention",
              "latent_unfolded_attention",
-             "latent_expand", "block_linear", "rglru_conv", "rglru_scan", "rglru_scan_chunks", "route", "routed_experts", "scale_")
+             "latent_expand", "block_linear", "rglru_conv", "rglru_scan", "rglru_scan_chunks", "route", "routed_experts", "scale_",
+             "embed_sum", "post_norm_add", "qk_norm_store", "linear_attention", "norm_gate", "glu_clamp", "softcap_")
 
     def __init__(self, kernels):
         self.k, self.records, self.saved = kernels, [], {}
@@ -608,6 +609,69 @@ class KernelTimes:
         return {n: {"calls": c, "ms": round(ms, 4)} for n, (c, ms) in sorted(out.items(), key=lambda kv: -kv[1][1])}
 
 
+def measure_prefill_and_decode(model, args, gen, flush):
+    """A prompt of ``args.prefill_tokens`` (median of three after two warm-up runs, L2 flushed before each) and steps
+    of ``args.batch`` single tokens at ``args.context`` (replayed graphs), each also once with every kernel call
+    between a pair of events."""
+    import torch
+
+    from pytorch_transformers_b200 import kernels
+    tokens, batch, context = args.prefill_tokens, args.batch, args.context
+    vocab = model.spec.vocab_size
+    prompt = torch.randint(0, vocab, (1, tokens), generator=gen).tolist()
+    cache = model.new_cache(max(tokens + 64, batch * ((context + args.steps + args.warmup + 70) // 64 * 64)))
+
+    def prefill_once():
+        s = cache.open()
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        model.step(cache, [s], prompt, want="last")
+        b.record()
+        torch.cuda.synchronize()
+        cache.close(s)
+        return a.elapsed_time(b)
+
+    times = [prefill_once() for _ in range(2 + 3)][2:]
+    with KernelTimes(kernels) as kt:
+        prefill_once()
+    pre_kernels = kt.table()
+    pre_ms = statistics.median(times)
+    # decode: `batch` sequences of `context` tokens, then single tokens
+    slots = [cache.open() for _ in range(batch)]
+    chunk = max(1, 8192 // context)
+    for i in range(0, batch, chunk):
+        ps = torch.randint(0, vocab, (len(slots[i:i + chunk]), context), generator=gen).tolist()
+        model.step(cache, slots[i:i + chunk], ps, want="last")
+    one = [[1]] * batch
+    for _ in range(args.warmup):
+        model.step(cache, slots, one, want="last")
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        model.step(cache, slots, one, want="last")
+    b.record()
+    torch.cuda.synchronize()
+    dec_ms = a.elapsed_time(b) / args.steps
+    graphs, model.use_graphs = model.use_graphs, False
+    with KernelTimes(kernels) as kt:
+        model.step(cache, slots, one, want="last")
+    dec_kernels = kt.table()
+    model.use_graphs = graphs
+    cache.close_all()
+    weights = model.weight_bytes()
+    out = {"prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(tokens / pre_ms * 1e3, 1),
+           "decode_ms_per_step": round(dec_ms, 4), "decode_tokens_per_s": round(batch / dec_ms * 1e3, 1),
+           "weight_GB": round(weights / 1e9, 3), "decode_weight_GBps": round(weights / dec_ms / 1e6, 1),
+           "prefill_kernels_ms": pre_kernels,
+           # launched one by one the decode step is paced by the host: these are upper bounds
+           "decode_kernels_ms": dec_kernels}
+    del cache
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_pafevik(args):
     import torch
 
@@ -626,59 +690,7 @@ def run_pafevik(args):
     result = {"only": "pafevik", "size": args.size, "prefill_tokens": tokens, "batch": batch, "context": context,
               "config": {"width": raw["width"], "layers": len(raw["layers"]), "heads": raw["layers"][0]["mixer"]["heads"]}}
     for name, model in models.items():
-        vocab = model.spec.vocab_size
-        prompt = torch.randint(0, vocab, (1, tokens), generator=gen).tolist()
-        cache = model.new_cache(max(tokens + 64, batch * ((context + args.steps + args.warmup + 70) // 64 * 64)))
-
-        def prefill_once():
-            s = cache.open()
-            flush.zero_()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            model.step(cache, [s], prompt, want="last")
-            b.record()
-            torch.cuda.synchronize()
-            cache.close(s)
-            return a.elapsed_time(b)
-
-        times = [prefill_once() for _ in range(2 + 3)][2:]
-        with KernelTimes(kernels) as kt:
-            prefill_once()
-        pre_kernels = kt.table()
-        pre_ms = statistics.median(times)
-        # decode: `batch` sequences of `context` tokens, then single tokens
-        slots = [cache.open() for _ in range(batch)]
-        chunk = max(1, 8192 // context)
-        for i in range(0, batch, chunk):
-            ps = torch.randint(0, vocab, (len(slots[i:i + chunk]), context), generator=gen).tolist()
-            model.step(cache, slots[i:i + chunk], ps, want="last")
-        one = [[1]] * batch
-        for _ in range(args.warmup):
-            model.step(cache, slots, one, want="last")
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(args.steps):
-            model.step(cache, slots, one, want="last")
-        b.record()
-        torch.cuda.synchronize()
-        dec_ms = a.elapsed_time(b) / args.steps
-        graphs, model.use_graphs = model.use_graphs, False
-        with KernelTimes(kernels) as kt:
-            model.step(cache, slots, one, want="last")
-        dec_kernels = kt.table()
-        model.use_graphs = graphs
-        cache.close_all()
-        weights = model.weight_bytes()
-        result[name] = {"prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(tokens / pre_ms * 1e3, 1),
-                        "decode_ms_per_step": round(dec_ms, 4), "decode_tokens_per_s": round(batch / dec_ms * 1e3, 1),
-                        "weight_GB": round(weights / 1e9, 3),
-                        "decode_weight_GBps": round(weights / dec_ms / 1e6, 1),
-                        "prefill_kernels_ms": pre_kernels,
-                        # launched one by one the decode step is paced by the host: these are upper bounds
-                        "decode_kernels_ms": dec_kernels}
-        del cache
-        torch.cuda.empty_cache()
+        result[name] = measure_prefill_and_decode(model, args, gen, flush)
     # the prompt's kernels against their rooflines (algorithmic FLOPs or bytes; a prompt's launches are paced by the
     # device, so the event pairs around them hold). The kernels of a step of single tokens are listed with their
     # device times under profiles/ (launch lists): launched one by one such a step is paced by the host.
@@ -728,9 +740,111 @@ def run_pafevik(args):
     return 0
 
 
+# ---- Zalunex beside Pafevik at equal size (`--only zalunex [--size s|m]`) ----
+# Sizes that resemble a served model's layers: the width; a pair mixer of 16 or 32 attention heads of 128 on a
+# quarter as many K/V heads with a window of 1,024, a sink and a gate, beside as many linear-attention heads of 128
+# with decays 1 - 2^-(3 + 5 h / heads); four layers whose feed-forwards take turns: a clamped gated unit 4 x the
+# width wide, then 64 plain experts of 1,408 of which a token uses 6. Pafevik beside it is `--only pafevik`'s model
+# of the same width, heads, layers and experts: the library's other design with a float32 stream, a per-sequence
+# state and routed experts.
+def zalunex_config(size):
+    z = PAFEVIK_SIZES[size]
+    w, heads = z["width"], z["heads"]
+    mixer = {"left": {"heads": heads, "kv_heads": heads // 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024}},
+             "right": {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * h / heads) for h in range(heads)]},
+             "left_scale": 1.0, "right_scale": 1.0}
+    glu = {"kind": "dense", "ff": 4 * w, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 64, "top": 6}}
+    return {"architecture": "Zalunex", "vocab": 32000, "width": w, "max_positions": 16384, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "logit_softcap": 30.0,
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": m} for m in (glu, moe, glu, moe)]}
+
+
+def run_zalunex(args):
+    import torch
+
+    import pytorch_transformers_b200 as ptb
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(0)
+    tokens, batch, context = args.prefill_tokens, args.batch, args.context
+    raw = zalunex_config(args.size)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    result = {"only": "zalunex", "size": args.size, "prefill_tokens": tokens, "batch": batch, "context": context,
+              "config": {"width": raw["width"], "layers": len(raw["layers"]), "heads": raw["layers"][0]["mixer"]["left"]["heads"]}}
+    for name, make in (("zalunex", lambda: ptb.AutoModelForCausalLM.from_config(ptb.ZalunexConfig.from_dict(raw), seed=0, dtype="bfloat16")),
+                       ("pafevik", lambda: ptb.AutoModelForCausalLM.from_config(ptb.PafevikConfig.from_dict(pafevik_config(args.size)),
+                                                                               seed=0, dtype="bfloat16"))):
+        model = make()
+        result[name] = measure_prefill_and_decode(model, args, gen, flush)
+        del model
+        torch.cuda.empty_cache()
+    # kernels of the prompt against their rooflines (algorithmic FLOPs or bytes over the time between the event pair
+    # around the call; a prompt's launches are paced by the device)
+    Z, P = result["zalunex"], result["pafevik"]
+    l, r, w = raw["layers"][0]["mixer"]["left"], raw["layers"][0]["mixer"]["right"], raw["width"]
+
+    def per_call(table, key):
+        return table[key]["ms"] / table[key]["calls"] if key in table else None
+
+    roof = {}
+    seen = sum(min(t + 1, l["mask"]["size"]) for t in range(tokens))        # (query, key) pairs inside the window
+    for key in ("attention_generic", "attention_mma"):
+        t = per_call(Z["prefill_kernels_ms"], key)
+        if t:
+            roof[f"sink_{key}_prefill_TFLOPs"] = round(l["heads"] * seen * 2 * (l["dim"] + l["vdim"]) / t / 1e9, 1)
+            roof[f"sink_{key}_prefill_frac_of_burst"] = round(roof[f"sink_{key}_prefill_TFLOPs"] / pk["bf16_tflops"], 4)
+    t = per_call(Z["prefill_kernels_ms"], "linear_attention")
+    if t:   # per chunk of 64: scores, scores x values, queries x state, keys x values
+        flops = r["heads"] * tokens * 2 * (64 * r["dim"] / 2 + 64 * r["vdim"] / 2 + 2 * r["dim"] * r["vdim"])
+        roof["linear_attention_prefill_TFLOPs"] = round(flops / t / 1e9, 1)
+        roof["linear_attention_prefill_frac_of_burst"] = round(roof["linear_attention_prefill_TFLOPs"] / pk["bf16_tflops"], 4)
+        io = tokens * r["heads"] * (2 * (2 * r["dim"] + r["vdim"]) + 4 * r["vdim"])      # q, k, v in; float32 rows out
+        roof["linear_attention_prefill_GBps"] = round(io / t / 1e6, 1)
+        roof["linear_attention_prefill_frac_of_hbm"] = round(roof["linear_attention_prefill_GBps"] / pk["hbm_gbs"], 4)
+    t = per_call(P["prefill_kernels_ms"], "rglru_scan_chunks")
+    if t:
+        R = pafevik_config(args.size)["layers"][1]["mixer"]["width"]
+        roof["pafevik_rglru_scan_prefill_GBps"] = round(tokens * R * (8 + 2 + 2 + 2) / t / 1e6, 1)
+        roof["pafevik_rglru_scan_prefill_frac_of_hbm"] = round(roof["pafevik_rglru_scan_prefill_GBps"] / pk["hbm_gbs"], 4)
+    pairs = tokens * 6
+    t = per_call(Z["prefill_kernels_ms"], "routed_experts")
+    if t:
+        roof["experts_prefill_TFLOPs"] = round(pairs * 2 * 2 * w * 1408 / t / 1e9, 1)
+        roof["experts_prefill_frac_of_burst"] = round(roof["experts_prefill_TFLOPs"] / pk["bf16_tflops"], 4)
+    t = per_call(P["prefill_kernels_ms"], "routed_experts")
+    if t:
+        roof["pafevik_experts_prefill_TFLOPs"] = round(pairs * 3 * 2 * w * 1408 / t / 1e9, 1)
+        roof["pafevik_experts_prefill_frac_of_burst"] = round(roof["pafevik_experts_prefill_TFLOPs"] / pk["bf16_tflops"], 4)
+    t = Z["prefill_kernels_ms"].get("matmul_nt")
+    if t:   # all library products of the prompt: the pairs' two products a layer, the gated units' two
+        n_in = (l["heads"] + l["kv_heads"]) * l["dim"] + l["kv_heads"] * l["vdim"] + l["heads"] + 2 * r["heads"] * (r["dim"] + r["vdim"])
+        n_out = l["heads"] * l["vdim"] + r["heads"] * r["vdim"]
+        flops = 2 * tokens * (4 * w * (n_in + n_out) + 2 * 3 * w * 4 * w)
+        roof["library_products_TFLOPs"] = round(flops / t["ms"] / 1e9, 1)
+        roof["library_products_frac_of_burst"] = round(roof["library_products_TFLOPs"] / pk["bf16_tflops"], 4)
+    for key, bytes_per_row in (("post_norm_add", w * (4 + 4 + 4 + 2)), ("norm_gate", r["heads"] * r["vdim"] * (4 + 2 + 2)),
+                               ("glu_clamp", 4 * w * (2 + 2 + 2)), ("qk_norm_store", (l["heads"] + 2 * l["kv_heads"]) * l["dim"] * 4)):
+        t = per_call(Z["prefill_kernels_ms"], key)
+        if t:
+            roof[f"{key}_prefill_GBps"] = round(tokens * bytes_per_row / t / 1e6, 1)
+            roof[f"{key}_prefill_frac_of_hbm"] = round(roof[f"{key}_prefill_GBps"] / pk["hbm_gbs"], 4)
+    t = per_call(P["prefill_kernels_ms"], "norm_stream")
+    if t:
+        roof["pafevik_norm_stream_prefill_GBps"] = round(tokens * w * (4 + 2) / t / 1e6, 1)
+        roof["pafevik_norm_stream_prefill_frac_of_hbm"] = round(roof["pafevik_norm_stream_prefill_GBps"] / pk["hbm_gbs"], 4)
+    result["roofline"] = roof
+    result["peaks"] = pk
+    print(json.dumps(result))
+    return 0
+
+
 def run_ours(args):
     if args.only == "pafevik":
         return run_pafevik(args)
+    if args.only == "zalunex":
+        return run_zalunex(args)
     if args.only == "sample":
         return run_sample(args)
     if args.only == "decode-attention":
@@ -1006,10 +1120,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "sample", "decode-attention", "prefill-attention", "config", "linear",
-                             "fill", "mma-cadence", "pafevik"],
+                             "fill", "mma-cadence", "pafevik", "zalunex"],
                     help="run one section only and print its numbers (for profilers)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape for --only decode / prefill")
-    ap.add_argument("--size", default="s", choices=sorted(PAFEVIK_SIZES), help="layer sizes for --only pafevik")
+    ap.add_argument("--size", default="s", choices=sorted(PAFEVIK_SIZES), help="layer sizes for --only pafevik and --only zalunex")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per sequence for --only decode")
     ap.add_argument("--past", type=int, default=0, help="cached tokens before the prompt for --only prefill-attention")

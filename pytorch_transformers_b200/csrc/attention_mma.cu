@@ -17,7 +17,32 @@ struct MmaParams {
   int heads, kv_heads, hpk, tokens_per_tile, n_splits;
   float scale;
   int window;
+  // optional (null / 1 / 0 for plain attention): a sink per head, exp(sink) in the softmax's denominator without key
+  // or value; a gate per (token, head), the head's output times sigmoid(gate[t * gate_stride + head]); a factor on
+  // everything; elements between two tokens' output rows (0: heads * D)
+  const float* sinks;
+  const __nv_bfloat16* gate;
+  int gate_stride;
+  float out_scale;
+  int out_stride;
+  // the softmax weights meet the values as two bfloat16 terms, the rounded weight and the rounded rest (16 bits of
+  // mantissa together), in two instructions: for designs that want their attention weights in 32-bit
+  int wide_weights;
 };
+
+// What a row's accumulated O is multiplied by at the end: 1 / (sum of the keys' weights + the sink's weight), the
+// gate and the factor. m, l: the row's running maximum (log2 units) and sum.
+__device__ __forceinline__ float finish_row(const MmaParams& p, float m, float l, int token, int head) {
+  float keep = 1.f;
+  if (p.sinks) {
+    const float s2 = p.sinks[head] * 1.4426950408889634f, m_all = fmaxf(m, s2);
+    keep = (m == -INFINITY) ? 0.f : exp2f(m - m_all);
+    l = l * keep + exp2f(s2 - m_all);
+  }
+  float f = (l > 0.f ? 1.f / l : 0.f) * keep * p.out_scale;
+  if (p.gate) f *= 1.f / (1.f + expf(-__bfloat162float(p.gate[size_t(token) * p.gate_stride + head])));
+  return f;
+}
 
 // q [n_tokens, heads, D]; out [n_tokens, heads * D] when part_o == nullptr, else partials:
 //   part_o [(tile, group chunk, split)][rows][D] float32 unnormalised, part_ml [...][rows][2] = (max, sum)
@@ -183,7 +208,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         m_run[i] = m_new;
       }
       // P = exp2(S - m), row sums, and P as A fragments for the second product
-      uint32_t pa[KEYS / 16][4];
+      uint32_t pa[KEYS / 16][4], pl[KEYS / 16][4];
       float l_blk[2] = {0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < KEYS / 8; ++j) {
@@ -196,6 +221,10 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         }
         pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);
         pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(pv[2], pv[3]);
+        if (p.wide_weights) {
+          pl[j >> 1][(j & 1) * 2 + 0] = pack_bf16(pv[0] - round_bf16(pv[0]), pv[1] - round_bf16(pv[1]));
+          pl[j >> 1][(j & 1) * 2 + 1] = pack_bf16(pv[2] - round_bf16(pv[2]), pv[3] - round_bf16(pv[3]));
+        }
       }
 #pragma unroll
       for (int i = 0; i < 2; ++i) l_run[i] = l_run[i] * corr[i] + l_blk[i];
@@ -214,6 +243,10 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
           ldmatrix_x4_trans(b0, b1, b2, b3, vs + swz<D>(kk * 16 + (m & 1) * 8 + (lane & 7), j + (m >> 1)));
           mma_bf16(o[j], pa[kk], b0, b1);
           mma_bf16(o[j + 1], pa[kk], b2, b3);
+          if (p.wide_weights) {
+            mma_bf16(o[j], pl[kk], b0, b1);
+            mma_bf16(o[j + 1], pl[kk], b2, b3);
+          }
         }
       }
       __syncthreads();  // the stage is free for the copy after next
@@ -230,9 +263,9 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       if (!row_ok[i]) continue;
-      const float inv = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
-      __nv_bfloat16* dst =
-          out + (size_t(start + q0 + row_tok[i]) * p.heads + (g * qpk + h0 + row_head[i])) * D + t4 * 2;
+      const int token = start + q0 + row_tok[i], head = g * qpk + h0 + row_head[i];
+      const float inv = finish_row(p, m_run[i], l_run[i], token, head);
+      __nv_bfloat16* dst = out + size_t(token) * p.out_stride + size_t(head) * D + t4 * 2;
 #pragma unroll
       for (int j = 0; j < D / 8; ++j)
         *reinterpret_cast<uint32_t*>(dst + j * 8) = pack_bf16(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
@@ -294,8 +327,9 @@ attention_mma_reduce_kernel(const float* __restrict__ part_o, const float* __res
       for (int e = 0; e < PER; ++e) acc[e] += po[e] * w;
     }
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  __nv_bfloat16* dst = out + (size_t(sb.seq_start[seq] + q0 + tok) * p.heads + (g * qpk + h0 + hh)) * D + lane * PER;
+  const int token = sb.seq_start[seq] + q0 + tok, head = g * qpk + h0 + hh;
+  const float inv = finish_row(p, m, l, token, head);
+  __nv_bfloat16* dst = out + size_t(token) * p.out_stride + size_t(head) * D + lane * PER;
 #pragma unroll
   for (int e = 0; e < PER; ++e) dst[e] = __float2bfloat16_rn(acc[e] * inv);
 }
@@ -352,12 +386,18 @@ PTB_API long long ptb_attention_mma_scratch_floats(int n_tiles, int heads, int k
 }
 
 // bfloat16 only. `warps` x 16 rows per tile; hpk * tokens_per_tile must equal warps * 16 or less.
-PTB_API int ptb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
+// sinks [heads] float32, gate (bfloat16, row t head h at gate[t * gate_stride + h]), out_scale and out_stride
+// (elements between two tokens' output rows; 0: heads * head_dim) and wide_weights as MmaParams says; null, null, 0, 1,
+// 0, 0: plain attention.
+PTB_API int ptb_attention_mma_gated(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
                               const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
                               const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
                               int tokens_per_tile, int n_splits, int warps, float scale, int window,
-                              cudaStream_t stream) {
+                              const float* sinks, const void* gate, int gate_stride, float out_scale, int out_stride,
+                              int wide_weights, cudaStream_t stream) {
   if (n_tiles <= 0) return PTB_OK;
+  if (out_stride == 0) out_stride = heads * head_dim;
+  if (out_stride < heads * head_dim || out_stride % 2 != 0 || (gate != nullptr && gate_stride < heads)) return PTB_ERR_SIZE;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || warps < 1 || warps > 8 || hpk < 1 ||
       tokens_per_tile < 1 || hpk * tokens_per_tile > warps * 16 || n_splits < 1 || n_splits > 65535)
     return PTB_ERR_SIZE;
@@ -368,6 +408,8 @@ PTB_API int ptb_attention_mma(const void* q, const void* k_pool, const void* v_p
   MmaParams p;
   p.heads = heads; p.kv_heads = kv_heads; p.hpk = hpk; p.tokens_per_tile = tokens_per_tile; p.n_splits = n_splits;
   p.scale = scale; p.window = window;
+  p.sinks = sinks; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride; p.out_scale = out_scale;
+  p.out_stride = out_stride; p.wide_weights = wide_weights;
   const long long o_floats = (long long)n_tiles * kv_heads * chunks * n_splits * (warps * 16) * head_dim;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + o_floats : nullptr;
@@ -381,6 +423,16 @@ PTB_API int ptb_attention_mma(const void* q, const void* k_pool, const void* v_p
     default:
       return PTB_ERR_SIZE;
   }
+}
+
+PTB_API int ptb_attention_mma(const void* q, const void* k_pool, const void* v_pool, void* out, float* scratch,
+                              const StepBatch* sb, const int* tile_seq, const int* tile_q0, int n_tiles,
+                              const float* alibi_slopes, int heads, int kv_heads, int head_dim, int hpk,
+                              int tokens_per_tile, int n_splits, int warps, float scale, int window,
+                              cudaStream_t stream) {
+  return ptb_attention_mma_gated(q, k_pool, v_pool, out, scratch, sb, tile_seq, tile_q0, n_tiles, alibi_slopes, heads,
+                                 kv_heads, head_dim, hpk, tokens_per_tile, n_splits, warps, scale, window, nullptr,
+                                 nullptr, 0, 1.f, 0, 0, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

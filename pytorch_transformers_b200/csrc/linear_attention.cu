@@ -11,6 +11,10 @@
 namespace {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+// an activated projection as the model dtype holds it (a bfloat16 model rounds it; float32 keeps it)
+template <typename T> __device__ __forceinline__ float act_as(float v, int act_silu) {
+  return act_silu ? to_f(from_f<T>(silu_f(v))) : v;
+}
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 
 // ------------------------------------------------------------------------------------------------
@@ -39,14 +43,11 @@ __global__ void linear_attention_scan_kernel(const T* __restrict__ proj, int str
     __syncthreads();    // the previous token's q and k are no longer read
     for (int d = threadIdx.x; d < dim; d += VB) {
       const float qv = to_f(row[h * dim + d]), kv = to_f(row[k_off + h * dim + d]);
-      qs[d] = act_silu ? silu_f(qv) : qv;
-      ks[d] = act_silu ? silu_f(kv) : kv;
+      qs[d] = act_as<T>(qv, act_silu);
+      ks[d] = act_as<T>(kv, act_silu);
     }
     float v = 0.f;
-    if (mine) {
-      v = to_f(row[v_off + h * v_dim + j]);
-      if (act_silu) v = silu_f(v);
-    }
+    if (mine) v = act_as<T>(to_f(row[v_off + h * v_dim + j]), act_silu);
     __syncthreads();
     float o = 0.f;
 #pragma unroll 4
@@ -59,6 +60,63 @@ __global__ void linear_attention_scan_kernel(const T* __restrict__ proj, int str
   }
   if (mine)
     for (int d = 0; d < dim; ++d) st[size_t(d) * v_dim + j] = S[d * VB + threadIdx.x];
+}
+
+// ------------------------------------------------------------------------------------------------
+// A step of single tokens: one block = one sequence x one head x a stretch of VJ value columns; the block's threads
+// are DS groups of VJ, thread (ds, j) owns rows ds, ds + DS, ... of column j of S, which it reads from the state area,
+// updates and writes back (each value is touched once, 32-byte sectors whole); the groups' partial sums
+// of o_j meet in shared memory in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(512)
+linear_attention_token_kernel(const T* __restrict__ proj, int stride, float* __restrict__ state, int state_stride,
+                              const int* __restrict__ slots, StepBatch sb, const float* __restrict__ decay,
+                              float* __restrict__ out, int heads, int dim, int v_dim, int act_silu, int VJ) {
+  extern __shared__ float sm[];
+  float* qs = sm;                 // [dim]
+  float* ks = qs + dim;           // [dim]
+  float* part = ks + dim;         // [DS][VJ]
+  const int DS = blockDim.x / VJ;
+  const int seq = blockIdx.x, h = blockIdx.y, jj = threadIdx.x % VJ, ds = threadIdx.x / VJ, j = blockIdx.z * VJ + jj;
+  const int t = sb.seq_start[seq];
+  const T* row = proj + size_t(t) * stride;
+  const int k_off = heads * dim, v_off = 2 * heads * dim;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    qs[d] = act_as<T>(to_f(row[h * dim + d]), act_silu);
+    ks[d] = act_as<T>(to_f(row[k_off + h * dim + d]), act_silu);
+  }
+  const bool mine = j < v_dim;
+  const float v = mine ? act_as<T>(to_f(row[v_off + h * v_dim + j]), act_silu) : 0.f;
+  const float a = decay[h];
+  __syncthreads();
+  float o = 0.f;
+  if (mine) {
+    float* col = state + size_t(slots[seq]) * state_stride + size_t(h) * dim * v_dim + j;
+    int d = ds;
+    for (; d + 3 * DS < dim; d += 4 * DS) {       // four rows in flight
+      float s[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) s[u] = col[size_t(d + u * DS) * v_dim];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        s[u] = fmaf(a, s[u], ks[d + u * DS] * v);
+        col[size_t(d + u * DS) * v_dim] = s[u];
+        o = fmaf(s[u], qs[d + u * DS], o);
+      }
+    }
+    for (; d < dim; d += DS) {
+      const float s = fmaf(a, col[size_t(d) * v_dim], ks[d] * v);
+      col[size_t(d) * v_dim] = s;
+      o = fmaf(s, qs[d], o);
+    }
+  }
+  part[ds * VJ + jj] = o;
+  __syncthreads();
+  if (ds == 0 && mine) {
+    float total = 0.f;
+    for (int g = 0; g < DS; ++g) total += part[g * VJ + jj];
+    out[(size_t(t) * heads + h) * v_dim + j] = total;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -94,13 +152,10 @@ __global__ void linear_attention_chunk_sum_kernel(const T* __restrict__ proj, in
     __syncthreads();
     for (int d = threadIdx.x; d < dim; d += VB) {
       const float kv = to_f(row[k_off + h * dim + d]);
-      ks[d] = act_silu ? silu_f(kv) : kv;
+      ks[d] = act_as<T>(kv, act_silu);
     }
     float v = 0.f;
-    if (mine) {
-      v = to_f(row[v_off + h * v_dim + j]);
-      if (act_silu) v = silu_f(v);
-    }
+    if (mine) v = act_as<T>(to_f(row[v_off + h * v_dim + j]), act_silu);
     __syncthreads();
 #pragma unroll 4
     for (int d = 0; d < dim; ++d) B[d * VB + threadIdx.x] = fmaf(a, B[d * VB + threadIdx.x], ks[d] * v);
@@ -126,14 +181,24 @@ __global__ void linear_attention_chunk_join_kernel(float* __restrict__ sums, flo
   const int n_new = sb.seq_new[seq], c0 = seq_chunk0[seq];
   float* st = state + size_t(slots[seq]) * state_stride + e;
   float s = *st;
-  for (int q0 = 0, c = c0; q0 < n_new; q0 += CH, ++c) {
-    const int n = min(CH, n_new - q0);
-    float* cell = sums + size_t(c) * per + e;
-    const float own = *cell;
-    *cell = s;
-    float an = 1.f;           // a^n by n multiplications: the same product as n single steps would apply
-    for (int i = 0; i < n; ++i) an *= a;
-    s = fmaf(an, s, own);
+  // a^n by n multiplications: the same product as n single steps would apply; n = CH for all chunks but the last
+  float a_full = 1.f, a_last = 1.f;
+  const int n_chunks = (n_new + CH - 1) / CH, n_last = n_new - (n_chunks - 1) * CH;
+  for (int i = 0; i < CH; ++i) {
+    a_full *= a;
+    if (i < n_last) a_last *= a;
+  }
+  constexpr int AHEAD = 8;      // chunks whose own sums are loaded before the chain of updates needs them
+  for (int g0 = 0; g0 < n_chunks; g0 += AHEAD) {
+    float own[AHEAD];
+#pragma unroll
+    for (int i = 0; i < AHEAD; ++i) own[i] = (g0 + i < n_chunks) ? sums[size_t(c0 + g0 + i) * per + e] : 0.f;
+#pragma unroll
+    for (int i = 0; i < AHEAD; ++i) {
+      if (g0 + i >= n_chunks) break;
+      sums[size_t(c0 + g0 + i) * per + e] = s;
+      s = fmaf(g0 + i == n_chunks - 1 ? a_last : a_full, s, own[i]);
+    }
   }
   *st = s;
 }
@@ -169,12 +234,8 @@ linear_attention_chunk_out_kernel(const T* __restrict__ proj, int stride, StepBa
     float qv = 0.f, kv = 0.f;
     if (i < n) {
       const T* row = proj + size_t(start + i) * stride;
-      qv = to_f(row[h * dim + d]);
-      kv = to_f(row[k_off + h * dim + d]);
-      if (act_silu) {
-        qv = silu_f(qv);
-        kv = silu_f(kv);
-      }
+      qv = act_as<T>(to_f(row[h * dim + d]), act_silu);
+      kv = act_as<T>(to_f(row[k_off + h * dim + d]), act_silu);
     }
     qs[i * (dim + 1) + d] = qv;
     ks[i * (dim + 1) + d] = kv;
@@ -202,8 +263,7 @@ linear_attention_chunk_out_kernel(const T* __restrict__ proj, int stride, StepBa
     float o = inter * pw[i + 1];
     const float* ar = A + i * (CH + 1);
     for (int s = 0; s <= i; ++s) {
-      float v = to_f(proj[size_t(start + s) * stride + v_off + h * v_dim + j]);
-      if (act_silu) v = silu_f(v);
+      const float v = act_as<T>(to_f(proj[size_t(start + s) * stride + v_off + h * v_dim + j]), act_silu);
       o = fmaf(ar[s], v, o);
     }
     out[(size_t(start + i) * heads + h) * v_dim + j] = o;
@@ -318,6 +378,30 @@ PTB_API int ptb_linear_attention_scan(int dtype, const void* proj, int stride, f
   return launch_status();
 }
 
+// The same for a step in which every sequence brings one token (the caller's word: `sb` is not read on the host).
+PTB_API int ptb_linear_attention_token(int dtype, const void* proj, int stride, float* state, int state_stride,
+                                       const int* slots, const StepBatch* sb, const float* decay, float* out, int heads,
+                                       int dim, int v_dim, int act, cudaStream_t stream) {
+  if (sb->n_tokens <= 0) return PTB_OK;
+  if (sb->n_tokens != sb->n_seqs) return PTB_ERR_SIZE;
+  if (heads <= 0 || heads > 65535 || dim <= 0 || v_dim <= 0 || stride < 2 * heads * dim + heads * v_dim || dim > 4096)
+    return PTB_ERR_SIZE;
+  const int threads = 512;
+  int vj = 32;
+  while (vj < 128 && vj < v_dim) vj *= 2;
+  const size_t smem = (2 * size_t(dim) + threads) * sizeof(float);
+  dim3 grid(sb->n_seqs, heads, (v_dim + vj - 1) / vj);
+  if (dtype == PTB_F32)
+    linear_attention_token_kernel<float><<<grid, threads, smem, stream>>>((const float*)proj, stride, state, state_stride,
+                                                                          slots, *sb, decay, out, heads, dim, v_dim, act, vj);
+  else if (dtype == PTB_BF16)
+    linear_attention_token_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(
+        (const __nv_bfloat16*)proj, stride, state, state_stride, slots, *sb, decay, out, heads, dim, v_dim, act, vj);
+  else
+    return PTB_ERR_DTYPE;
+  return launch_status();
+}
+
 PTB_API int ptb_linear_attention_chunk_tokens() { return CH; }
 
 // Does the chunked form take these sizes (its third pass holds a chunk's queries, keys and scores in shared memory)?
@@ -360,6 +444,19 @@ PTB_API int ptb_linear_attention_chunks(int dtype, const void* proj, int stride,
   else if (dtype == PTB_BF16) PTB_LA_CHUNKS(__nv_bfloat16)
   else return PTB_ERR_DTYPE;
 #undef PTB_LA_CHUNKS
+  return launch_status();
+}
+
+// pass 2 alone (the tensor-core passes 1 and 3 are in csrc/linear_attention_mma.cu)
+PTB_API int ptb_linear_attention_chunk_join(float* sums, float* state, int state_stride, const int* slots,
+                                            const StepBatch* sb, const int* seq_chunk0, const float* decay, int heads,
+                                            int dim, int v_dim, cudaStream_t stream) {
+  if (sb->n_tokens <= 0) return PTB_OK;
+  if (heads <= 0 || dim <= 0 || v_dim <= 0 || sb->n_seqs > 65535) return PTB_ERR_SIZE;
+  const size_t per = size_t(heads) * dim * v_dim;
+  dim3 grid(unsigned((per + 255) / 256), sb->n_seqs);
+  linear_attention_chunk_join_kernel<<<grid, 256, 0, stream>>>(sums, state, state_stride, slots, *sb, seq_chunk0, decay,
+                                                               heads, dim, v_dim);
   return launch_status();
 }
 

@@ -96,7 +96,9 @@ def lib():
                      "ptb_latent_attention_mma_supports", "ptb_rglru_scan_chunks", "ptb_block_epilogue", "ptb_latent_gather",
                      "ptb_latent_unfold", "ptb_latent_q_unfold", "ptb_gate_heads", "ptb_linear_attention_scan",
                      "ptb_linear_attention_chunks", "ptb_linear_attention_chunks_supports", "ptb_norm_gate",
-                     "ptb_qk_norm_store", "ptb_post_norm_add", "ptb_embed_sum", "ptb_softcap", "ptb_glu_clamp"):
+                     "ptb_qk_norm_store", "ptb_post_norm_add", "ptb_embed_sum", "ptb_softcap", "ptb_glu_clamp",
+                     "ptb_attention_mma_gated", "ptb_linear_attention_chunk_join", "ptb_linear_attention_mma_supports",
+                     "ptb_linear_attention_chunks_mma", "ptb_linear_attention_token"):
             getattr(L, name).restype = ctypes.c_int
         L.ptb_latent_part_floats.restype = ctypes.c_longlong
         L.ptb_expert_plan_words.restype = ctypes.c_longlong
@@ -465,25 +467,37 @@ def attention_mma_supports(head_dim: int) -> bool:
 def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatchC,
                   tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, slopes: Optional[torch.Tensor],
                   kv_heads: int, scale: float, window: int, tokens_per_tile: int, heads_per_tile: int, warps: int,
-                  n_splits: int, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  n_splits: int, scratch: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                  gate: Optional[torch.Tensor] = None, out_scale: float = 1.0,
+                  out: Optional[torch.Tensor] = None, wide_weights: bool = False) -> torch.Tensor:
     """Tensor-core attention over the paged cache (bfloat16). A tile holds ``tokens_per_tile`` tokens
     x ``heads_per_tile`` heads of one K/V group in ``warps`` x 16 rows; with ``n_splits`` > 1 the key
-    pages are divided among blocks and joined by a second kernel (``scratch``: float32 workspace)."""
-    _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes, scratch)
+    pages are divided among blocks and joined by a second kernel (``scratch``: float32 workspace).
+    ``sinks``, ``gate``, ``out_scale``, ``out``: as attention_generic takes them. ``wide_weights``: the softmax
+    weights meet the values as two bfloat16 terms (16 bits of mantissa) instead of one."""
+    _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes, scratch, sinks)
     if q.dtype != torch.bfloat16:
         raise KernelError("attention_mma takes bfloat16 tensors")
     n, heads, head_dim = q.shape
-    out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((n, heads * head_dim), dtype=q.dtype, device=q.device)
+    _check_rows(out, (n, heads * head_dim), q.dtype, "attention_mma: out")
+    if gate is not None:
+        _check_rows(gate, (n, heads), q.dtype, "attention_mma: gate")
+    if out.data_ptr() % 4 or out.stride(0) % 2:
+        raise KernelError("attention_mma: output rows must start at whole 32-bit words")
     if n_splits > 1:
         need = attention_mma_scratch_floats(n_tiles, heads, kv_heads, heads_per_tile, n_splits, warps, head_dim)
         if scratch is None:
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)
         elif scratch.numel() < need or scratch.dtype != torch.float32:
             raise KernelError(f"attention_mma: scratch of {need} float32 values needed")
-    _check(lib().ptb_attention_mma(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch),
-                                   ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
-                                   heads, kv_heads, head_dim, heads_per_tile, tokens_per_tile, n_splits, warps,
-                                   ctypes.c_float(scale), window, _stream(q)), "attention_mma")
+    _check(lib().ptb_attention_mma_gated(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch),
+                                         ctypes.byref(batch), _ptr(tile_seq), _ptr(tile_q0), n_tiles, _ptr(slopes),
+                                         heads, kv_heads, head_dim, heads_per_tile, tokens_per_tile, n_splits, warps,
+                                         ctypes.c_float(scale), window, _ptr(sinks), _ptr(gate),
+                                         0 if gate is None else gate.stride(0), ctypes.c_float(out_scale), out.stride(0),
+                                         1 if wide_weights else 0, _stream(q)), "attention_mma")
     if n_splits > 1:
         global launches
         launches += 1   # the kernel that joins the splits
@@ -987,13 +1001,21 @@ def linear_attention_chunks_supports(dim: int, v_dim: int) -> bool:
     return bool(lib().ptb_linear_attention_chunks_supports(dim, v_dim))
 
 
+def linear_attention_mma_takes(proj: torch.Tensor, dim: int, v_dim: int) -> bool:
+    """Do the tensor-core passes of the chunked form take this projection (bfloat16, sizes of 64 or 128, rows and the
+    q, k, v parts at whole 16-byte words)?"""
+    return (proj.dtype == torch.bfloat16 and bool(lib().ptb_linear_attention_mma_supports(dim, v_dim))
+            and proj.data_ptr() % 16 == 0 and proj.stride(0) % 8 == 0)
+
+
 def linear_attention(proj: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, batch: StepBatchC, decay: torch.Tensor,
-                     heads: int, dim: int, v_dim: int, act: str = "silu", chunks=None) -> torch.Tensor:
+                     heads: int, dim: int, v_dim: int, act: str = "silu", chunks=None, single_tokens: bool = False) -> torch.Tensor:
     """Per head S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over the step's tokens, continuing and leaving
     each sequence's S [heads, dim, v_dim] in ``state`` [slots, heads * dim * v_dim] (float32; rows may lie wider
     apart). ``proj`` [tokens, >= 2 heads dim + heads v_dim] holds q, k, v side by side (rows may lie wider apart);
     ``act`` "silu" is applied to all three as they are read. ``chunks``: (chunk_seq, chunk_q0, seq_chunk0, n_chunks)
-    for the chunked form (prompts), None for the token-by-token form. Returns float32 [tokens, heads * v_dim]."""
+    for the chunked form (prompts), None for the token-by-token form; ``single_tokens``: every sequence of the step
+    brings one token (the state is then updated where it lies). Returns float32 [tokens, heads * v_dim]."""
     _need_cuda(decay, slots)
     n = proj.shape[0]
     if state.dtype != torch.float32 or state.shape[1] != heads * dim * v_dim or state.stride(1) != 1:
@@ -1003,6 +1025,11 @@ def linear_attention(proj: torch.Tensor, state: torch.Tensor, slots: torch.Tenso
         raise KernelError("linear_attention: act is 'none' or 'silu'; decay is float32 [heads]")
     out = torch.empty((n, heads * v_dim), dtype=torch.float32, device=proj.device)
     code, a = _dtype_code(proj), 1 if act == "silu" else 0
+    if single_tokens:
+        _check(lib().ptb_linear_attention_token(code, _ptr(proj), proj.stride(0), _ptr(state), state.stride(0), _ptr(slots),
+                                                ctypes.byref(batch), _ptr(decay), _ptr(out), heads, dim, v_dim, a,
+                                                _stream(proj)), "linear_attention_token")
+        return out
     if chunks is None:
         _check(lib().ptb_linear_attention_scan(code, _ptr(proj), proj.stride(0), _ptr(state), state.stride(0), _ptr(slots),
                                                ctypes.byref(batch), _ptr(decay), _ptr(out), heads, dim, v_dim, a,
@@ -1010,11 +1037,22 @@ def linear_attention(proj: torch.Tensor, state: torch.Tensor, slots: torch.Tenso
         return out
     chunk_seq, chunk_q0, seq_chunk0, n_chunks = chunks
     sums = torch.empty((n_chunks, heads, dim, v_dim), dtype=torch.float32, device=proj.device)
+    global launches
+    if linear_attention_mma_takes(proj, dim, v_dim):
+        # bfloat16 with keys and values of 64 or 128: passes 1 and 3 on the tensor cores, pass 2 as it is
+        L, stream, args = lib(), _stream(proj), (ctypes.byref(batch), _ptr(chunk_seq), _ptr(chunk_q0), n_chunks, _ptr(decay))
+        _check(L.ptb_linear_attention_chunks_mma(0, _ptr(proj), proj.stride(0), *args, _ptr(sums), None, heads, dim, v_dim, a,
+                                                 stream), "linear_attention_chunks_mma (sums)")
+        _check(L.ptb_linear_attention_chunk_join(_ptr(sums), _ptr(state), state.stride(0), _ptr(slots), ctypes.byref(batch),
+                                                 _ptr(seq_chunk0), _ptr(decay), heads, dim, v_dim, stream),
+               "linear_attention_chunk_join")
+        _check(L.ptb_linear_attention_chunks_mma(1, _ptr(proj), proj.stride(0), *args, _ptr(sums), _ptr(out), heads, dim, v_dim,
+                                                 a, stream), "linear_attention_chunks_mma (outputs)")
+        return out
     _check(lib().ptb_linear_attention_chunks(code, _ptr(proj), proj.stride(0), _ptr(state), state.stride(0), _ptr(slots),
                                              ctypes.byref(batch), _ptr(chunk_seq), _ptr(chunk_q0), _ptr(seq_chunk0),
                                              n_chunks, _ptr(decay), _ptr(sums), _ptr(out), heads, dim, v_dim, a,
                                              _stream(proj)), "linear_attention_chunks")
-    global launches
     launches += 2       # three kernels
     return out
 

@@ -94,9 +94,36 @@ class SinkAttention(Part):
                             self.vdim, self.eps, write_cache=entry.writes_cache)
         gate = proj[:, self.in_rows() - self.heads:] if self.has_gate else None
         tiles = ctx.plan(AttentionTiles.plan_key)
+        if (q.dtype == torch.bfloat16 and self.dim == self.vdim and k.attention_mma_supports(self.dim)
+                and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
+            # bfloat16 with a head size of the tensor-core kernel: tiles of tokens x heads of a K/V group; a step of
+            # single tokens divides each sequence's visible pages among blocks that a second kernel joins
+            tokens = tiles.facts["mma_tokens"]
+            q_per_kv = self.heads // self.kv_heads
+            if tokens == 1:
+                hpk = min(q_per_kv, 128)
+                warps, splits = (hpk + 15) // 16, self._decode_splits(ctx, hpk)
+            else:
+                warps, splits = 8, 1
+                hpk = max(1, min(q_per_kv, 128 // tokens))
+            k.attention_mma(q, k_pool, v_pool, batch, tiles.dev["mtile_seq"], tiles.dev["mtile_q0"], tiles.facts["n_mma_tiles"],
+                            None, self.kv_heads, self.scale, self.window, tokens, hpk, warps, splits, sinks=self.p_sink,
+                            gate=gate, out_scale=out_scale, out=out, wide_weights=True)
+            return
         k.attention_generic(q, k_pool, v_pool, batch, tiles.dev["tile_seq"], tiles.dev["tile_q0"], tiles.facts["n_tiles"],
                             None, self.kv_heads, self.scale, self.window, sinks=self.p_sink, gate=gate, out_scale=out_scale,
                             out=out)
+
+    def _decode_splits(self, ctx, hpk: int) -> int:
+        """Blocks per (sequence, K/V head) in a step of single tokens: enough to fill the device, each with two
+        pages of visible keys at least."""
+        k = self.build.kernels
+        q_per_kv = self.heads // self.kv_heads
+        blocks = ctx.n_seqs * self.kv_heads * ((q_per_kv + hpk - 1) // hpk)
+        pages = ctx.pages_hint
+        if self.window > 0:
+            pages = min(pages, self.window // k.PAGE + 2)
+        return max(1, min((2 * k.sm_count(self.build.device)) // blocks, pages // 2, 64))
 
     def forward(self, x, ctx, entry):
         k = self.build.kernels

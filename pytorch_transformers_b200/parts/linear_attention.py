@@ -87,7 +87,7 @@ class LinearAttention(Part):
         if plan.facts["n_chunks"] and k.linear_attention_chunks_supports(self.dim, self.vdim):
             chunks = (plan.dev["chunk_seq"], plan.dev["chunk_q0"], plan.dev["seq_chunk0"], plan.facts["n_chunks"])
         o = k.linear_attention(proj, state, ctx.dev["slots"], ctx.batch_c[0], self.decay, self.heads, self.dim, self.vdim,
-                               self.activation, chunks)
+                               self.activation, chunks, single_tokens=ctx.is_decode)
         n = self.out_columns()
         gate = proj[:, self.in_rows() - n:] if self.has_gate else None
         k.norm_gate(o, self.p_norm, gate, self.eps, proj.dtype, out_scale, out=out)

@@ -54,7 +54,12 @@ class MixerPair(Part):
 
     def after_bind(self) -> None:
         """Both children's input projections in one matrix, their output projections side by side."""
-        self.p_in = torch.cat([self.left.in_weight(), self.right.in_weight()]).contiguous()
+        rows = [self.left.in_weight(), self.right.in_weight()]
+        # the right child's part of the projection starts at a whole 16-byte word (kernels that load 16 bytes at a time)
+        self.pad = (-self.left.in_rows()) % 8
+        if self.pad:
+            rows.insert(1, torch.zeros((self.pad, rows[0].shape[1]), dtype=rows[0].dtype, device=rows[0].device))
+        self.p_in = torch.cat(rows).contiguous()
         self.p_out = torch.cat([self.left.out_weight(), self.right.out_weight()], dim=1).contiguous()
         self.left.release_projections()
         self.right.release_projections()
@@ -68,5 +73,5 @@ class MixerPair(Part):
         cols_l, cols_r = self.left.out_columns(), self.right.out_columns()
         heads = torch.empty((x.shape[0], cols_l + cols_r), dtype=x.dtype, device=x.device)
         self.left.forward_projected(proj[:, :rows_l], ctx, entry, heads[:, :cols_l], self.scales[0])
-        self.right.forward_projected(proj[:, rows_l:], ctx, entry, heads[:, cols_l:], self.scales[1])
+        self.right.forward_projected(proj[:, rows_l + self.pad:], ctx, entry, heads[:, cols_l:], self.scales[1])
         return linear(k, heads, w_out, wide_out=True)

@@ -197,14 +197,14 @@ def test_attention_with_window_sink_and_gate(dtype, m):
         close(torch.cat(got[i]), refs[i], dtype, f"sequence {i}", bf16=2e-2)
 
 
-def needle_case(dtype, window, query_pos, key_pos, past):
+def needle_case(dtype, window, query_pos, key_pos, past, d=32, vd=24):
     """One head on one K/V head with unit gains, and W_q = W_k P for a permutation P of the input's entries: a query
     whose input is P^T times an earlier token's input has that token's key as its query, score = scale * dim, while
     all other keys (its own too) score far lower. The sequence runs as a prompt of ``past`` tokens and the rest in
     one step (or token by token when the rest is short). Returns (the mixer's rows, the plain rows, the needle's value
     row times the query's gate through W_o)."""
-    width, d, vd = 40, 32, 24
-    m = zm.left(1, 1, d, vd, window, scale=1.5)      # an aligned key scores 48, others about 1.5 * sqrt(32) * N(0, 1)
+    width = 40
+    m = zm.left(1, 1, d, vd, window, scale=48.0 / d)      # an aligned key scores 48, others about 48 / sqrt(d) * N(0, 1)
     w = left_weights(m, width, 11, dtype)
     P = torch.eye(width, dtype=torch.float64)[torch.roll(torch.arange(width), 7)]
     w["mix.left.q"] = w["mix.left.k"] @ P
@@ -234,22 +234,23 @@ def needle_case(dtype, window, query_pos, key_pos, past):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,vd", [(32, 24), (64, 64)])        # the general kernel; the tensor-core kernel (bfloat16)
 @pytest.mark.parametrize("window,query_pos,past", [(33, 200, 0), (33, 200, 150), (33, 200, 200), (64, 191, 0), (64, 192, 192),
                                                    (65, 130, 128), (130, 400, 399), (130, 400, 0), (1, 70, 70), (2, 64, 64),
                                                    (500, 450, 449), (500, 450, 0), (7, 6, 0), (7, 7, 4)])
-def test_attention_sees_the_window_and_not_one_key_more(dtype, window, query_pos, past):
+def test_attention_sees_the_window_and_not_one_key_more(dtype, window, query_pos, past, d, vd):
     """The aligned key sits at the window's last place (distance window - 1: seen) and one further (distance
     window: not seen), or at the first token when the window is longer than the sequence; as part of a prompt
     and as a single token; across page borders."""
     tol = 1e-4 if dtype == "float32" else 3e-2
     inside = max(0, query_pos - (window - 1))
-    got, ref, needle = needle_case(dtype, window, query_pos, inside, past)
+    got, ref, needle = needle_case(dtype, window, query_pos, inside, past, d, vd)
     close(got, ref, dtype, "key at the window's edge", bf16=2e-2)
     if inside < query_pos:          # the needle is not the query itself: the row is the needle's value
         assert row_errors(got[-1:], needle[None]).max() < tol
     outside = query_pos - window
     if outside >= 0:
-        got, ref, needle = needle_case(dtype, window, query_pos, outside, past)
+        got, ref, needle = needle_case(dtype, window, query_pos, outside, past, d, vd)
         close(got, ref, dtype, "key just outside the window", bf16=2e-2)
         assert row_errors(got[-1:], needle[None]).max() > 0.2
 
@@ -269,7 +270,8 @@ def test_a_heavy_sink_takes_the_weight(dtype):
 
 
 RIGHTS = [zm.right(3, 16, 24, [0.5, 0.9, 0.999]), zm.right(2, 6, 10, [1.0, 0.0]), zm.right(1, 8, 8, [0.97]),
-          zm.right(4, 32, 64, [0.9, 0.99, 0.999, 0.6]), zm.right(2, 128, 128, [0.999, 0.95]), zm.right(2, 72, 40, [0.98, 0.8])]
+          zm.right(4, 32, 64, [0.9, 0.99, 0.999, 0.6]), zm.right(2, 128, 128, [0.999, 0.95]), zm.right(2, 72, 40, [0.98, 0.8]),
+          zm.right(2, 64, 128, [1.0, 0.5]), zm.right(3, 128, 64, [0.9, 0.0, 0.999]), zm.right(1, 64, 64, [0.99])]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
