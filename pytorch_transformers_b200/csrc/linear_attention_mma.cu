@@ -24,14 +24,8 @@ __device__ __forceinline__ void split_pack(float x, float y, uint32_t& hi, uint3
   lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
-// 8 activated values of a projection row (16-byte load), as float32 rounded to bfloat16
-__device__ __forceinline__ void load_act8(const __nv_bfloat16* src, bool ok, int act_silu, float (&f)[8]) {
-  if (!ok) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = 0.f;
-    return;
-  }
-  const uint4 w = *reinterpret_cast<const uint4*>(src);
+// 8 values of a projection row (one 16-byte word) activated: float32 values rounded to bfloat16
+__device__ __forceinline__ void act8(const uint4& w, int act_silu, float (&f)[8]) {
   unpack_bf16x8(w, f);
   if (act_silu) {
 #pragma unroll
@@ -39,18 +33,30 @@ __device__ __forceinline__ void load_act8(const __nv_bfloat16* src, bool ok, int
   }
 }
 
-// Stage rows [0, CH) x D columns of an activated projection into a swizzled [CH][D] tile; rows >= n are zero.
-template <int D>
-__device__ __forceinline__ void stage_act(unsigned char* tile, const __nv_bfloat16* first_row, int stride, int n,
-                                          int act_silu, int tid, int nthreads) {
-  constexpr int CHUNKS = D / 8;
-  for (int i = tid; i < CH * CHUNKS; i += nthreads) {
-    const int row = i / CHUNKS, c = i % CHUNKS;
-    float f[8];
-    load_act8(first_row + size_t(row) * stride + c * 8, row < n, act_silu, f);
-    *reinterpret_cast<uint4*>(tile + swz<D>(row, c)) = pack_bf16x8(f);
+// The 16-byte words of rows [0, CH) x D columns of a projection that thread `tid` of NT stages: all loads are issued
+// before the first is used (rows >= n read as zero, which silu keeps).
+template <int D, int NT>
+struct StagedWords {
+  static constexpr int CHUNKS = D / 8, PER = CH * CHUNKS / NT;
+  uint4 w[PER];
+  __device__ __forceinline__ void load(const __nv_bfloat16* first_row, int stride, int n, int tid) {
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int i = tid + u * NT, row = i / CHUNKS, c = i % CHUNKS;
+      w[u] = row < n ? *reinterpret_cast<const uint4*>(first_row + size_t(row) * stride + c * 8) : make_uint4(0, 0, 0, 0);
+    }
   }
-}
+  // activated, into a swizzled [CH][D] tile
+  __device__ __forceinline__ void store(unsigned char* tile, int act_silu, int tid) const {
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int i = tid + u * NT, row = i / CHUNKS, c = i % CHUNKS;
+      float f[8];
+      act8(w[u], act_silu, f);
+      *reinterpret_cast<uint4*>(tile + swz<D>(row, c)) = pack_bf16x8(f);
+    }
+  }
+};
 
 // ------------------------------------------------------------------------------------------------ pass 1
 // One block = one chunk x one head; DK / 16 warps, warp w owns rows 16 w .. 16 w + 15 of B [DK, DV].
@@ -75,15 +81,19 @@ la_chunk_sum_mma_kernel(const __nv_bfloat16* __restrict__ proj, int stride, Step
       p *= a;
     }
   }
-  __syncthreads();
   const __nv_bfloat16* row0 = proj + size_t(start) * stride;
+  StagedWords<DK, DK * 2> kw;
+  StagedWords<DV, DK * 2> vw;
+  kw.load(row0 + heads * DK + h * DK, stride, n, tid);
+  vw.load(row0 + 2 * heads * DK + h * DV, stride, n, tid);
+  __syncthreads();
   {
     constexpr int CHUNKS = DK / 8;
-    const __nv_bfloat16* k0 = row0 + heads * DK + h * DK;
-    for (int i = tid; i < CH * CHUNKS; i += DK * 2) {
-      const int row = i / CHUNKS, cc = i % CHUNKS;
+#pragma unroll
+    for (int u = 0; u < kw.PER; ++u) {
+      const int i = tid + u * DK * 2, row = i / CHUNKS, cc = i % CHUNKS;
       float f[8];
-      load_act8(k0 + size_t(row) * stride + cc * 8, row < n, act_silu, f);
+      act8(kw.w[u], act_silu, f);
       const float w = row < n ? pw[n - 1 - row] : 0.f;
       uint4 hi, lo;
       split_pack(f[0] * w, f[1] * w, hi.x, lo.x);
@@ -94,7 +104,7 @@ la_chunk_sum_mma_kernel(const __nv_bfloat16* __restrict__ proj, int stride, Step
       *reinterpret_cast<uint4*>(k_lo + swz<DK>(row, cc)) = lo;
     }
   }
-  stage_act<DV>(v_s, row0 + 2 * heads * DK + h * DV, stride, n, act_silu, tid, DK * 2);
+  vw.store(v_s, act_silu, tid);
   __syncthreads();
 
   float acc[DV / 8][4];
@@ -158,23 +168,40 @@ la_chunk_out_mma_kernel(const __nv_bfloat16* __restrict__ proj, int stride, Step
     }
   }
   const __nv_bfloat16* row0 = proj + size_t(start) * stride;
-  stage_act<DK>(q_s, row0 + h * DK, stride, n, act_silu, tid, 256);
-  stage_act<DK>(k_s, row0 + heads * DK + h * DK, stride, n, act_silu, tid, 256);
-  stage_act<DV>(v_s, row0 + 2 * heads * DK + h * DV, stride, n, act_silu, tid, 256);
+  {
+    StagedWords<DK, 256> qw, kw;
+    StagedWords<DV, 256> vw;
+    qw.load(row0 + h * DK, stride, n, tid);
+    kw.load(row0 + heads * DK + h * DK, stride, n, tid);
+    vw.load(row0 + 2 * heads * DK + h * DV, stride, n, tid);
+    qw.store(q_s, act_silu, tid);
+    kw.store(k_s, act_silu, tid);
+    vw.store(v_s, act_silu, tid);
+  }
   {
     const float* S0 = before + (size_t(c) * heads + h) * DK * DV;
-    constexpr int CHUNKS = DV / 8;
-    for (int i = tid; i < DK * CHUNKS; i += 256) {
-      const int row = i / CHUNKS, cc = i % CHUNKS;
-      const float4 x = *reinterpret_cast<const float4*>(S0 + size_t(row) * DV + cc * 8);
-      const float4 y = *reinterpret_cast<const float4*>(S0 + size_t(row) * DV + cc * 8 + 4);
-      uint4 hi, lo;
-      split_pack(x.x, x.y, hi.x, lo.x);
-      split_pack(x.z, x.w, hi.y, lo.y);
-      split_pack(y.x, y.y, hi.z, lo.z);
-      split_pack(y.z, y.w, hi.w, lo.w);
-      *reinterpret_cast<uint4*>(s_hi + swz<DV>(row, cc)) = hi;
-      *reinterpret_cast<uint4*>(s_lo + swz<DV>(row, cc)) = lo;
+    constexpr int CHUNKS = DV / 8, PER = DK * CHUNKS / 256, BATCH = PER < 4 ? PER : 4;
+    static_assert(PER % BATCH == 0, "the state's words divide among the threads in whole batches");
+#pragma unroll
+    for (int u0 = 0; u0 < PER; u0 += BATCH) {
+      float4 x[BATCH], y[BATCH];
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int i = tid + (u0 + u) * 256, row = i / CHUNKS, cc = i % CHUNKS;
+        x[u] = *reinterpret_cast<const float4*>(S0 + size_t(row) * DV + cc * 8);
+        y[u] = *reinterpret_cast<const float4*>(S0 + size_t(row) * DV + cc * 8 + 4);
+      }
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int i = tid + (u0 + u) * 256, row = i / CHUNKS, cc = i % CHUNKS;
+        uint4 hi, lo;
+        split_pack(x[u].x, x[u].y, hi.x, lo.x);
+        split_pack(x[u].z, x[u].w, hi.y, lo.y);
+        split_pack(y[u].x, y[u].y, hi.z, lo.z);
+        split_pack(y[u].z, y[u].w, hi.w, lo.w);
+        *reinterpret_cast<uint4*>(s_hi + swz<DV>(row, cc)) = hi;
+        *reinterpret_cast<uint4*>(s_lo + swz<DV>(row, cc)) = lo;
+      }
     }
   }
   __syncthreads();

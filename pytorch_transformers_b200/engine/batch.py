@@ -113,6 +113,7 @@ class StepContext:
             raise StepError(f"a slot is named twice in one step: {list(slots)}")
         self.cache = cache
         self.side_stream = None     # set by the engine for steps of a few tokens (see parts/block.py)
+        self.next_block = None      # set by the engine before every block: the block that runs after it
         self._rope: dict = {}
         self.keep_alive: list = []  # tensors that must outlive the step's last kernel on another stream
         self.slots = [int(s) for s in slots]

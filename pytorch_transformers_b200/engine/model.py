@@ -388,8 +388,10 @@ class CausalLM:
             x = self.embedding_norm.forward(x)
         if self.spec.stream_float32 and x.dtype != torch.float32:
             x = k.to_float(x)       # from here to the final norm the stream is float32
-        for entry in self.schedule:
-            x = self.blocks[entry.block].forward(x, ctx, entry)   # a tensor, or a DeferredSum of two branches
+        for i, entry in enumerate(self.schedule):
+            # the block that runs next, for blocks that can form its opening norm in their own last kernel
+            ctx.next_block = self.blocks[self.schedule[i + 1].block] if i + 1 < len(self.schedule) else None
+            x = self.blocks[entry.block].forward(x, ctx, entry)   # a tensor, a DeferredSum of two branches or a NormedStream
         x = resolve(k, x)
         if ctx.n_wanted == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)

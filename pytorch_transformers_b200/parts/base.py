@@ -19,7 +19,9 @@ engine.batch.StepContext of the running step; ``x`` is [tokens, hidden] in the m
                      ``planner()`` (per-step arrays of its own) and ``runs_beside(ctx)``.
 * ``feed_forward``:  ``forward(x, ctx) -> y``.
 * ``block``:         ``forward(x, ctx, entry) -> x'`` from its child parts; ``x`` and ``x'`` may be a
-                     ``DeferredSum`` (two terms whose sum the next norm forms); ``resolve`` gives the tensor.
+                     ``DeferredSum`` (two terms whose sum the next norm forms) or a ``NormedStream`` (a stream with
+                     the next block's opening norm already formed); ``resolve`` gives the tensor. ``ctx.next_block``
+                     is the block that runs next (None after the last).
 
 Every part declares its parameters in ``param_decls()`` (logical name -> ParamDecl) and
 receives them in ``bind(tensors)``.
@@ -159,8 +161,20 @@ class DeferredSum:
             self.stream = None
 
 
+@dataclasses.dataclass
+class NormedStream:
+    """A residual stream together with its norm by one norm part (``by``), which the block before computed in the
+    kernel that formed the stream because it knew which block runs next (``ctx.next_block``). The block that owns
+    ``by`` uses ``normed``; anybody else takes ``stream``."""
+    stream: Any
+    normed: Any
+    by: Any
+
+
 def resolve(kernels, x):
-    """The tensor that ``x`` stands for (``x`` itself, or the sum of a DeferredSum)."""
+    """The tensor that ``x`` stands for (``x`` itself, the sum of a DeferredSum, the stream of a NormedStream)."""
+    if isinstance(x, NormedStream):
+        return x.stream
     if isinstance(x, DeferredSum):
         x.join(x.base.device)
         return kernels.residual(x.base, x.pending)

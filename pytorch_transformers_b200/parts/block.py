@@ -12,7 +12,7 @@ Sums are formed in float32 and rounded once; where the model keeps its residual 
 """
 from __future__ import annotations
 
-from .base import BuildContext, DeferredSum, Part, PartSpec, register_part, resolve
+from .base import BuildContext, DeferredSum, NormedStream, Part, PartSpec, register_part, resolve
 
 
 def _plus(kernels, part, base, *args):
@@ -113,7 +113,8 @@ class SandwichBlock(Part):
 
     on a float32 residual stream (``ModelSpec.stream_float32``). All four norms are RMS norms. The closing norm of
     the mixer's result, the stream's sum and the feed-forward's opening norm are one kernel; so are the closing norm
-    of the feed-forward's result and the sum. A block without ``feed_forward`` ends after its first half."""
+    of the feed-forward's result and the sum, which also forms the opening norm of the next block when that is a
+    sandwich block too (``NormedStream``). A block without ``feed_forward`` ends after its first half."""
     graph_safe = True
 
     def __init__(self, build: BuildContext, spec: PartSpec, mult: float = 1.0):
@@ -130,13 +131,24 @@ class SandwichBlock(Part):
     def forward(self, x, ctx, entry):
         import torch
         k = self.build.kernels
+        opened = x.normed if isinstance(x, NormedStream) and x.by is self.norm_mixer else None
         x = resolve(k, x)
         if x.dtype != torch.float32:
             raise ValueError("the sandwich block runs on a float32 residual stream")
-        y = self.mixer.forward(self.norm_mixer.forward(x), ctx, entry)
+        y = self.mixer.forward(opened if opened is not None else self.norm_mixer.forward(x), ctx, entry)
         if self.feed_forward is None:
-            return k.post_norm_add(x, y, self.post_mixer.p_weight, self.post_mixer.eps, self.mult)
+            return self._close(ctx, x, y, self.post_mixer)
         x, h = k.post_norm_add(x, y, self.post_mixer.p_weight, self.post_mixer.eps, self.mult,
                                gain_next=self.norm_ff.p_weight, eps_next=self.norm_ff.eps, next_dtype=self.build.dtype)
-        y = self.feed_forward.forward(h, ctx)
-        return k.post_norm_add(x, y, self.post_ff.p_weight, self.post_ff.eps, self.mult)
+        return self._close(ctx, x, self.feed_forward.forward(h, ctx), self.post_ff)
+
+    def _close(self, ctx, x, y, post):
+        """The block's last sum; with the next block's opening norm when that block is of this kind."""
+        k = self.build.kernels
+        nxt = getattr(ctx, "next_block", None)
+        if isinstance(nxt, SandwichBlock):
+            norm = nxt.norm_mixer
+            x, h = k.post_norm_add(x, y, post.p_weight, post.eps, self.mult, gain_next=norm.p_weight, eps_next=norm.eps,
+                                   next_dtype=self.build.dtype)
+            return NormedStream(x, h, norm)
+        return k.post_norm_add(x, y, post.p_weight, post.eps, self.mult)
