@@ -132,8 +132,8 @@ __global__ void split_rotate_store_kernel(const T* __restrict__ fused, T* __rest
 // score(q at position p, key at position j) = (q . k_j + alibi_h(j)) * scale for j <= p
 // (and j > p - window when window > 0); softmax over those keys in float32; out = sum p_j v_j.
 // Values may have a size of their own (v_dim; the V pool is [pages][kv_heads][PTB_PAGE][v_dim]).
-// With `sinks` [heads] the softmax's denominator also holds exp(sink_h): a term without key or value,
-// not scaled, counted once per row. With `gate` (row t, head h at gate[t * gate_stride + h]) the head's
+// With `sinks` [heads] every row's softmax denominator holds one more term, exp(sink_h), taken as stored
+// (`scale` is not applied to it); no key or value is read for it. With `gate` (row t, head h at gate[t * gate_stride + h]) the head's
 // output is multiplied by sigmoid(gate); `out_scale` multiplies everything. Output row t, head h starts
 // at out[t * out_stride + h * v_dim].
 template <typename T>

@@ -17,8 +17,8 @@ struct MmaParams {
   int heads, kv_heads, hpk, tokens_per_tile, n_splits;
   float scale;
   int window;
-  // optional (null / 1 / 0 for plain attention): a sink per head, exp(sink) in the softmax's denominator without key
-  // or value; a gate per (token, head), the head's output times sigmoid(gate[t * gate_stride + head]); a factor on
+  // optional (null / 1 / 0 for plain attention): a sink per head, one more term exp(sink) of the softmax's denominator for which
+  // nothing is read; a gate per (token, head), the head's output times sigmoid(gate[t * gate_stride + head]); a factor on
   // everything; elements between two tokens' output rows (0: heads * D)
   const float* sinks;
   const __nv_bfloat16* gate;

@@ -243,8 +243,8 @@ def attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                       sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, out_scale: float = 1.0,
                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of the step's tokens over the paged cache; returns [tokens, heads * v_dim] (v_dim is
-    the V pool's row size). ``sinks`` [heads] float32: a term exp(sink) in every row's softmax denominator
-    that has no key and no value. ``gate`` [tokens, heads] (a view whose rows may be wider apart): each head's
+    the V pool's row size). ``sinks`` [heads] float32: one more term exp(sink) in every row's softmax denominator,
+    for which nothing is read. ``gate`` [tokens, heads] (a view whose rows may be wider apart): each head's
     output times sigmoid(gate). ``out``: a [tokens, heads * v_dim] view (rows may be wider apart) to write into."""
     _need_cuda(q, k_pool, v_pool, tile_seq, tile_q0, slopes, sinks)
     n, heads, head_dim = q.shape

@@ -4,8 +4,8 @@
 * no position in the scores, or a rotation from a ``position`` child (not built here: the scores of this
   mixer carry no position);
 * a sliding window: position i sees j with 0 <= i - j < window (0: all earlier positions);
-* a sink: a learned number per head whose exponential is added to the softmax's denominator; it has no key
-  and no value, is not scaled and counts once;
+* a sink: one learned logit per head that takes part in the softmax's normalisation only: ``exp(sink)`` is one
+  more term of the denominator, used as stored (``scale`` does not touch it), and nothing is read for it;
 * an output gate: head h's result times sigmoid(W_g x)_h, one number per head, read from the mixer's input;
 * values of a size of their own (``vdim``).
 

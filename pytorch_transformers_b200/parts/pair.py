@@ -1,4 +1,4 @@
-"""Two mixers side by side on the same input: ``left_scale * left(h) + right_scale * right(h)``.
+"""A mixer made of two: both children read the pair's input ``h`` and the result is ``left_scale * left(h) + right_scale * right(h)``.
 
 Each child is a mixer that can run in two halves around its own projections (the *projected* protocol):
 

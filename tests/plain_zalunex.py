@@ -51,7 +51,7 @@ def sink_window_attention(h, w, p, m, eps):
 
 def lightning_attention(h, w, p, m, eps, state=None):
     """Linear attention with a fixed decay per head: S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t.
-    The heads side by side are RMS-normed together, gated and projected. ``state`` [heads, dim, vdim]
+    All heads' outputs form one row that is RMS-normed as a whole, then gated and projected. ``state`` [heads, dim, vdim]
     continues an earlier part of the sequence; returns (output, state after the last token)."""
     H, d, vd = m["heads"], m["dim"], m["vdim"]
     T = h.shape[0]
@@ -105,7 +105,8 @@ def moe_scaled_input(h, w, p, mlp):
 
 
 def layer_order(cfg):
-    """The layer indices in the order they run: layers start..stop-1 run ``times`` times in a row."""
+    """The layer indices in running order: the stretch [start, stop) of the list is gone through ``times`` times
+    before the layers after it follow."""
     n = len(cfg["layers"])
     loop = cfg.get("loop")
     if not loop:

@@ -4,8 +4,8 @@ The configurations differ from one another in every size: head counts and groupi
 that differ from each other and are no multiple of 8, windows shorter than a page, longer than a page and
 longer than any prompt, decays from 0 to 1, layer order, which stretch of layers runs again and how often,
 layers without a feed-forward, router shapes. "ones" sets to 1 what can be 1 (heads, window, experts, top,
-the loop's times, the residual multiplier). Weights are drawn so that every tensor matters: norm weights
-around zero (the gain is one plus the weight), sinks of the scores' own size, gains around one.
+the loop's times, the residual multiplier). Weights are drawn so that every tensor matters: the layers' norm weights are
+near 0 (their gain is 1 + weight), sinks are as large as scores are, plain gains lie around 1.
 """
 from __future__ import annotations
 
